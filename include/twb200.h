@@ -1,0 +1,102 @@
+/* C ABI of libtwb200: B200 (sm_100a) kernels for ThunderWorld's selective-FP4-repair path.
+ *
+ * Conventions (same as the reference's CUTLASS bridge,
+ * packages/fp4-repair/src/thunderworld_fp4/cutlass/fused.cu:65-88 and cutlass/backend.py:48-71):
+ *   - every pointer is a device pointer owned by the caller unless it is an argument struct;
+ *   - the library allocates nothing, keeps no state between calls and never synchronises;
+ *   - `stream` is a raw cudaStream_t; every call is legal inside CUDA Graph stream capture;
+ *   - the return value is 0 on success, otherwise a code that tw_status() turns into text;
+ *   - no C++ exception crosses the boundary.
+ *
+ * NVFP4 operand format (reference: thunderworld_fp4/cosmos/calibration.py:24-54):
+ *   codes   uint8 [planes, rows, K/2]   two E2M1 values per byte, even k in the low nibble
+ *   scales  uint8 [planes, rows, K/16]  E4M3 bytes, one per 16 consecutive k, row-major
+ *   factor  float                        one per tensor (max|x| / 2688, 1.0 for an all-zero tensor)
+ * plane 0 = base, plane 1 = residual of the same tensor under the same factor.
+ * "atom layout" of a scale matrix [rows, K/16] (rows padded to a multiple of 128):
+ *   offset(r, c) = (r/128)*128*(K/16) + (c/4)*512 + (r%32)*16 + ((r%128)/32)*4 + c%4
+ * (reference: cutlass/packing.py:24-25), the layout block-scaled tensor-core MMAs read.
+ */
+#ifndef TWB200_H
+#define TWB200_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status ------------------------------------------------------------------------------ */
+/* Replaces tw_status of cutlass/fused.cu:86-88. Never returns NULL. */
+const char* tw_status(int status);
+/* Library ABI version (bumped when a struct below changes). */
+int tw_abi_version(void);
+
+/* ---- activation quantizer ------------------------------------------------------------------
+ * One call replaces the reference's launch chain scaled_amax -> finish_amax -> pack_activation
+ * (thunderworld_fp4/linear.py:13-25, _linear_kernels.py:8-56), its calibrated twin
+ * (_calibrated.py:60-71), the current-residual selector base_summary -> choose -> residual_only
+ * (_sparse_pack.py:77-93) and the direct atom-layout scale producer (cutlass/packing.py:85-109).
+ */
+typedef struct TwQuantizeArgs {
+  const void* x;            /* bf16 [m, k], contiguous */
+  const float* prescale;    /* [k] multiplied in before bf16 rounding, or NULL for ones */
+  const float* sensitivity; /* [k], selector weights (repair == 3), else NULL */
+  float* factor;            /* out: tensor factor; in when factor_given != 0 */
+  const float* wg;          /* optional: weight global scale, to emit alpha = factor * wg */
+  float* alpha;             /* optional out (needs wg) */
+  uint8_t* codes;           /* out [planes, mp, k/2] */
+  uint8_t* scales;          /* out [planes, mp, k/16] row-major E4M3 bytes */
+  uint8_t* scales_swz;      /* optional out [planes, ceil(m/128)*128, k/16] atom layout */
+  uint8_t* mask;            /* bool bytes [ceil(m/128), k/128]: in for repair == 2, out for repair == 3 */
+  void* workspace;          /* tw_quantize_workspace(m, k) bytes of scratch */
+  int m, k, mp;             /* mp = ceil(m/16)*16 */
+  int repair;               /* 0 base plane only; 1 residual everywhere; 2 residual where mask is set,
+                               zero codes and scales elsewhere; 3 residual everywhere and mask := the
+                               top-`na` K128 blocks per M128 row block ranked by residual energy */
+  int na;                   /* quota for repair == 3 (0 < na < k/128) */
+  int factor_given;         /* nonzero: read *factor instead of reducing max|x| */
+  float base, res, gain;    /* scale multipliers of the calibrated packer; 1,1,1 = plain */
+  float energy;             /* < 1: energy-prefix stop of the selector; 1 = off */
+} TwQuantizeArgs;
+size_t tw_quantize_workspace(int m, int k);
+int tw_quantize(const TwQuantizeArgs* args, void* stream);
+
+/* Row-major E4M3 scale bytes [rows, cols] -> atom layout [ceil(rows/128)*128, cols], padding zeroed.
+ * Replaces thunderworld_fp4/cutlass/layout.py:7-25 (swizzle). cols % 4 == 0. */
+int tw_swizzle_scales(const uint8_t* src, int rows, int cols, uint8_t* dst, void* stream);
+
+/* ---- fused repair GEMM ---------------------------------------------------------------------
+ * out[m, n] (bf16) = alpha * ( A0 W0^T + sum_{kb in support(mb)} A1[kb] W0[kb]^T
+ *                            + sum_{(nb,kb) in tiles} A0[kb] W1[nb,kb]^T
+ *                            [+ A1[kb] W1[nb,kb]^T where both are selected, if cross] )
+ * with one fp32 accumulator per output element and one bf16 rounding.
+ * Same entry point, argument order and meaning as tw_fused of cutlass/fused.cu:78-85 and its
+ * tcgen05 twin tools/thor_handoff/cutlass_sm110_fused.cu:57-77. The struct below starts with the
+ * reference's RepairIO (cutlass/repair_collective.cuh:5-10, bank_blocks from
+ * tools/thor_handoff/sm110_repair_collective.cuh:6-11) and appends the atom-layout scale pointers
+ * of the residual operands, which this implementation requires whenever those terms are issued.
+ */
+typedef struct TwRepairIO {
+  const uint8_t *ac, *as, *wc, *ws, *wr, *wrs; /* activation codes/scales (planes), W0 codes/scales,
+                                                  W1 bank codes [slots,128,64] / scales [slots,128,8] */
+  const int32_t *wi, *off, *wloc;              /* CSR over N128 blocks: k-block per slot, row offsets
+                                                  [n/128+1], bank position per slot */
+  const uint8_t* mask;                         /* bool [ceil(m/128), k/128], read at run time */
+  int32_t m, mp, n, k, na, hasw, cross, shared, dense, bank_blocks;
+  /* extensions */
+  const uint8_t* a1s_swz;  /* residual-plane activation scales, atom layout [ceil(m/128)*128, k/16] */
+  const uint8_t* wrs_swz;  /* W1 bank scales, atom layout per tile: [slots][1024] */
+} TwRepairIO;
+/* Bytes of caller-owned workspace (holds the device status word; zero it once). */
+size_t tw_workspace(int m, int n, int k);
+int tw_fused(int m, int n, int k, const void* a_codes, const void* w_codes, const void* sfa_swz,
+             const void* sfb_swz, void* out_bf16, const float* alpha_dev, void* workspace, void* stream,
+             const TwRepairIO* io);
+/* Number of tcgen05 MMA instructions (128 x BN x 64) the last-described problem issues; host-side
+ * helper for the issued-work ledger (thunderworld_fp4/cosmos/budget.py:36-67). Pure function. */
+int tw_fused_tile_n(int n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

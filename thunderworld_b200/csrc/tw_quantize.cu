@@ -1,0 +1,292 @@
+// Activation quantizer: bf16 [M,K] -> NVFP4 base plane A0 and residual plane A1 = A - deq(A0),
+// both as E2M1 codes + E4M3 per-16 scales under one fp32 tensor factor, with the block scales
+// written row-major (parity artefact, consumed by nothing on the GPU) and in the 128x4 atom layout
+// the block-scaled MMA reads. Arithmetic follows the reference encoder operation by operation
+// (thunderworld_fp4/cosmos/calibration.py:30-54, _quantize.py:81-107, _calibrated.py:11-38):
+// IEEE fp32 division, E4M3 and E2M1 round-to-nearest-even, residual taken from the rounded base.
+#include "tw_common.cuh"
+#include "../../include/twb200.h"
+
+namespace {
+
+constexpr int TILE = 128;          // rows and columns of one CTA tile (the repair lattice)
+constexpr int PACK_THREADS = 256;  // 32 rows x 8 groups of 16 per pass, 4 passes
+
+struct PackParams {
+  const __nv_bfloat16* x;
+  const float* prescale;
+  const float* sensitivity;
+  float* factor;
+  const float* wg;
+  float* alpha;
+  uint8_t* codes;
+  uint8_t* scales;
+  uint8_t* scales_swz;
+  const uint8_t* mask;
+  const unsigned* amax_bits;
+  float* scores;
+  int m, k, mp, mb;
+  int repair, factor_given;
+  float base, res, gain;
+};
+
+__device__ __forceinline__ float load_factor(const PackParams& p) {
+  if (p.factor_given) return *p.factor;
+  float peak = __uint_as_float(*p.amax_bits);
+  return peak > 0.f ? __fdiv_rn(peak, 2688.f) : 1.f;
+}
+
+// max |bf16(x * d)| over the tensor, as the bit pattern of a non-negative float.
+template <bool PRESCALE>
+__global__ void __launch_bounds__(256) amax_kernel(const uint4* __restrict__ x, const float* __restrict__ d,
+                                                   long long vecs, int k, unsigned* __restrict__ out) {
+  float peak = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < vecs;
+       i += (long long)gridDim.x * blockDim.x) {
+    uint4 v = __ldg(x + i);
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    int col = (int)((i * 8) % k);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float lo = tw::bf16_bits_to_float(w[j] & 0xffffu), hi = tw::bf16_bits_to_float(w[j] >> 16);
+      if (PRESCALE) {
+        lo = __bfloat162float(__float2bfloat16_rn(__fmul_rn(lo, __ldg(d + col + 2 * j))));
+        hi = __bfloat162float(__float2bfloat16_rn(__fmul_rn(hi, __ldg(d + col + 2 * j + 1))));
+      }
+      peak = fmaxf(peak, fmaxf(fabsf(lo), fabsf(hi)));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, o));
+  if ((threadIdx.x & 31) == 0 && peak > 0.f) atomicMax(out, __float_as_uint(peak));
+}
+
+// One group of 16 values: scale byte + 8 code bytes; optionally the dequantized values.
+__device__ __forceinline__ uint32_t encode_group(const float (&z)[16], float multiplier, uint2& codes,
+                                                 float& scale_value) {
+  float peak = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) peak = fmaxf(peak, fabsf(z[i]));
+  float raw = __fdiv_rn(__fmul_rn(peak, multiplier), 6.f);
+  raw = fminf(fmaxf(raw, 0.001953125f), 448.f);
+  uint32_t sb = tw::f32_to_e4m3(raw);
+  float s = tw::e4m3_to_f32(sb);
+  uint32_t w[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint32_t b = tw::f32x2_to_e2m1x2(__fdiv_rn(z[2 * i], s), __fdiv_rn(z[2 * i + 1], s));
+    w[i >> 2] |= b << (8 * (i & 3));
+  }
+  codes = make_uint2(w[0], w[1]);
+  scale_value = s;
+  return sb;
+}
+
+__device__ __forceinline__ uint32_t scale_offset(int row, int col, int cols) {
+  return (uint32_t)(row >> 7) * 128u * cols + (uint32_t)(col >> 2) * 512u + (uint32_t)(row & 31) * 16u +
+         (uint32_t)((row & 127) >> 5) * 4u + (uint32_t)(col & 3);
+}
+
+// grid (K/128, ceil(M/128)); each CTA packs one 128x128 tile of the lattice.
+template <bool PRESCALE>
+__global__ void __launch_bounds__(PACK_THREADS) pack_kernel(PackParams p) {
+  __shared__ float warp_scores[PACK_THREADS / 32];
+  const int kb = blockIdx.x, mbi = blockIdx.y;
+  const int t = threadIdx.x, cg = t & 7, r0 = t >> 3;
+  const int col = kb * TILE + cg * 16;
+  const float f = load_factor(p);
+  const int kbn = p.k / TILE;
+  const int cols16 = p.k / 16;
+  const bool planes2 = p.repair != 0;
+  const bool active = p.repair != 2 || p.mask[mbi * kbn + kb] != 0;
+  float dsc[16], sens[16];
+  if (PRESCALE) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) dsc[i] = __ldg(p.prescale + col + i);
+  }
+  if (p.repair == 3) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) sens[i] = __ldg(p.sensitivity + col + i);
+  }
+  float score = 0.f;
+#pragma unroll 1
+  for (int pass = 0; pass < 4; ++pass) {
+    const int row = mbi * TILE + pass * 32 + r0;
+    float y[16];
+    if (row < p.m) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.x + (size_t)row * p.k + col);
+      uint4 a = __ldg(src), b = __ldg(src + 1);
+      uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        y[2 * i] = tw::bf16_bits_to_float(w[i] & 0xffffu);
+        y[2 * i + 1] = tw::bf16_bits_to_float(w[i] >> 16);
+      }
+      if (PRESCALE) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) y[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(y[i], dsc[i])));
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) y[i] = 0.f;
+    }
+    float z[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) z[i] = __fdiv_rn(y[i], f);
+    uint2 c0, c1 = make_uint2(0u, 0u);
+    float s0, s1;
+    uint32_t sb0 = encode_group(z, p.base, c0, s0), sb1 = 0u;
+    if (planes2) {
+      float r[16];
+      const uint32_t w[2] = {c0.x, c0.y};
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        uint32_t code = (w[i >> 3] >> (4 * (i & 7))) & 15u;
+        float deq = __fmul_rn(tw::e2m1_value(code), s0);
+        r[i] = __fsub_rn(z[i], deq);
+        if (p.repair == 3) {
+          float e = __fsub_rn(y[i], __fmul_rn(deq, f));
+          score = __fadd_rn(score, __fmul_rn(__fmul_rn(e, e), sens[i]));
+        }
+      }
+      if (active) {
+        sb1 = encode_group(r, p.res, c1, s1);
+        if (p.gain != 1.f) sb1 = tw::f32_to_e4m3(fminf(__fmul_rn(s1, p.gain), 448.f));
+      }
+    }
+    if (row >= p.mp) { sb0 = 0u; sb1 = 0u; }
+    // gather the 8 scale bytes of this row's K128 block into lanes cg == 0 (all) and cg == 4 (upper half)
+    uint32_t lo0 = sb0, lo1 = sb1;
+#pragma unroll
+    for (int j = 1; j < 4; ++j) {
+      lo0 |= __shfl_down_sync(0xffffffffu, sb0, j) << (8 * j);
+      lo1 |= __shfl_down_sync(0xffffffffu, sb1, j) << (8 * j);
+    }
+    uint32_t hi0 = __shfl_down_sync(0xffffffffu, lo0, 4), hi1 = __shfl_down_sync(0xffffffffu, lo1, 4);
+    if (row < p.mp) {
+      size_t ci = (size_t)row * (p.k / 2) + kb * 64 + cg * 8;
+      *reinterpret_cast<uint2*>(p.codes + ci) = c0;
+      if (planes2) *reinterpret_cast<uint2*>(p.codes + (size_t)p.mp * (p.k / 2) + ci) = c1;
+      if (cg == 0) {
+        size_t si = (size_t)row * cols16 + kb * 8;
+        *reinterpret_cast<uint2*>(p.scales + si) = make_uint2(lo0, hi0);
+        if (planes2) *reinterpret_cast<uint2*>(p.scales + (size_t)p.mp * cols16 + si) = make_uint2(lo1, hi1);
+      }
+    }
+    if (p.scales_swz && (cg & 3) == 0) {
+      uint32_t off = scale_offset(row, kb * 8 + cg, cols16);
+      *reinterpret_cast<uint32_t*>(p.scales_swz + off) = lo0;
+      if (planes2) *reinterpret_cast<uint32_t*>(p.scales_swz + (size_t)p.mb * 128 * cols16 + off) = lo1;
+    }
+  }
+  if (p.repair == 3) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) score = __fadd_rn(score, __shfl_xor_sync(0xffffffffu, score, o));
+    if ((t & 31) == 0) warp_scores[t >> 5] = score;
+    __syncthreads();
+    if (t == 0) {
+      float total = 0.f;
+      for (int w = 0; w < PACK_THREADS / 32; ++w) total = __fadd_rn(total, warp_scores[w]);
+      p.scores[mbi * kbn + kb] = total;
+    }
+  }
+  if (blockIdx.x == 0 && blockIdx.y == 0 && t == 0) {
+    if (!p.factor_given) *p.factor = f;
+    if (p.alpha && p.wg) *p.alpha = __fmul_rn(f, *p.wg);
+  }
+}
+
+// Per M128 row block: rank K128 blocks by score (descending, lower index wins ties), keep rank < na,
+// optionally stop at the shortest prefix holding `energy` of the total (_sparse_pack.py:46-61).
+__global__ void __launch_bounds__(128) choose_kernel(const float* __restrict__ scores, uint8_t* __restrict__ mask,
+                                                     int kbn, int na, float energy) {
+  extern __shared__ float row[];
+  const int mb = blockIdx.x;
+  for (int j = threadIdx.x; j < kbn; j += blockDim.x) row[j] = scores[mb * kbn + j];
+  __syncthreads();
+  float total = 0.f;
+  if (energy < 1.f)
+    for (int j = 0; j < kbn; ++j) total = __fadd_rn(total, row[j]);
+  for (int j = threadIdx.x; j < kbn; j += blockDim.x) {
+    const float mine = row[j];
+    int rank = 0;
+    for (int o = 0; o < kbn; ++o) rank += (row[o] > mine) || (row[o] == mine && o < j);
+    bool keep = rank < na;
+    if (keep && energy < 1.f) {
+      float before = 0.f;
+      for (int o = 0; o < kbn; ++o)
+        if ((row[o] > mine) || (row[o] == mine && o < j)) before = __fadd_rn(before, row[o]);
+      keep = before < __fmul_rn(energy, total);
+    }
+    mask[mb * kbn + j] = keep ? 1 : 0;
+  }
+}
+
+__global__ void __launch_bounds__(256) swizzle_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                                      int rows, int cols, int rows_padded) {
+  // one thread per 4 consecutive scale columns of one row
+  const int quads = cols >> 2;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= (long long)rows_padded * quads) return;
+  int row = (int)(i / quads), q = (int)(i % quads);
+  uint32_t v = row < rows ? *reinterpret_cast<const uint32_t*>(src + (size_t)row * cols + q * 4) : 0u;
+  *reinterpret_cast<uint32_t*>(dst + scale_offset(row, q * 4, cols)) = v;
+}
+
+}  // namespace
+
+extern "C" size_t tw_quantize_workspace(int m, int k) {
+  if (m <= 0 || k <= 0) return 0;
+  size_t mb = (size_t)(m + 127) / 128, kb = (size_t)(k + 127) / 128;
+  return 256 + mb * kb * sizeof(float);
+}
+
+extern "C" int tw_quantize(const TwQuantizeArgs* a, void* stream_) {
+  if (!a || !a->x || !a->codes || !a->scales || !a->factor || !a->workspace) return TW_ERR_ARGUMENT;
+  if (a->m <= 0 || a->k <= 0) return TW_ERR_ARGUMENT;
+  if (a->k % 128 || a->mp != (a->m + 15) / 16 * 16) return TW_ERR_SHAPE;
+  if (a->repair < 0 || a->repair > 3) return TW_ERR_ARGUMENT;
+  if ((a->repair == 2 || a->repair == 3) && !a->mask) return TW_ERR_ARGUMENT;
+  if (a->repair == 3 && (!a->sensitivity || a->na <= 0 || a->na >= a->k / 128)) return TW_ERR_ARGUMENT;
+  if (!(a->base > 0.f) || !(a->res > 0.f) || !(a->gain > 0.f)) return TW_ERR_ARGUMENT;
+  const uintptr_t align = (uintptr_t)a->x | (uintptr_t)a->codes | (uintptr_t)a->scales |
+                          (uintptr_t)a->scales_swz | (uintptr_t)a->workspace;
+  if (align & 15) return TW_ERR_ALIGNMENT;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  unsigned* amax = static_cast<unsigned*>(a->workspace);
+  float* scores = reinterpret_cast<float*>(static_cast<char*>(a->workspace) + 256);
+  const int mb = (a->m + 127) / 128, kb = a->k / 128;
+  if (!a->factor_given) {
+    if (cudaMemsetAsync(amax, 0, sizeof(unsigned), stream) != cudaSuccess) return TW_ERR_LAUNCH;
+    long long vecs = (long long)a->m * a->k / 8;
+    int blocks = (int)((vecs + 255) / 256 < 148 * 8 ? (vecs + 255) / 256 : 148 * 8);
+    if (a->prescale)
+      amax_kernel<true><<<blocks, 256, 0, stream>>>(static_cast<const uint4*>(a->x), a->prescale, vecs, a->k, amax);
+    else
+      amax_kernel<false><<<blocks, 256, 0, stream>>>(static_cast<const uint4*>(a->x), nullptr, vecs, a->k, amax);
+  }
+  PackParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(a->x);
+  p.prescale = a->prescale; p.sensitivity = a->sensitivity;
+  p.factor = a->factor; p.wg = a->wg; p.alpha = a->alpha;
+  p.codes = a->codes; p.scales = a->scales; p.scales_swz = a->scales_swz; p.mask = a->mask;
+  p.amax_bits = amax; p.scores = scores;
+  p.m = a->m; p.k = a->k; p.mp = a->mp; p.mb = mb;
+  p.repair = a->repair; p.factor_given = a->factor_given;
+  p.base = a->base; p.res = a->res; p.gain = a->gain;
+  dim3 grid(kb, mb);
+  if (a->prescale) pack_kernel<true><<<grid, PACK_THREADS, 0, stream>>>(p);
+  else pack_kernel<false><<<grid, PACK_THREADS, 0, stream>>>(p);
+  if (a->repair == 3) choose_kernel<<<mb, 128, kb * sizeof(float), stream>>>(scores, a->mask, kb, a->na, a->energy);
+  return cudaGetLastError() == cudaSuccess ? TW_OK : TW_ERR_LAUNCH;
+}
+
+extern "C" int tw_swizzle_scales(const uint8_t* src, int rows, int cols, uint8_t* dst, void* stream_) {
+  if (!src || !dst || rows <= 0 || cols <= 0) return TW_ERR_ARGUMENT;
+  if (cols % 4) return TW_ERR_SHAPE;
+  if (((uintptr_t)src | (uintptr_t)dst) & 3) return TW_ERR_ALIGNMENT;
+  const int rp = (rows + 127) / 128 * 128;
+  long long work = (long long)rp * (cols / 4);
+  swizzle_kernel<<<(unsigned)((work + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(src, dst, rows, cols, rp);
+  return cudaGetLastError() == cudaSuccess ? TW_OK : TW_ERR_LAUNCH;
+}

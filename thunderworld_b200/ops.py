@@ -1,0 +1,153 @@
+"""Thin torch-facing wrappers: pass data_ptr()s and the current stream to the C ABI.
+
+Host-side mirror of the reference's packers and launch wrappers:
+  _pack                 thunderworld_fp4/linear.py:13-25
+  pack (calibrated)     thunderworld_fp4/_calibrated.py:60-71
+  pack_sparse           thunderworld_fp4/_sparse_pack.py:77-93
+  pack_with_factor      thunderworld_fp4/_fusion.py:37-42
+  pack_input / swizzle  thunderworld_fp4/cutlass/packing.py:85-109, cutlass/layout.py:16-25
+  CutlassFused.run_packed  thunderworld_fp4/cutlass/backend.py:48-71
+torch is used for device memory and streams only.
+"""
+import ctypes
+from dataclasses import dataclass
+import torch
+from . import _lib
+
+
+def cdiv(a, b):
+    return (a + b - 1) // b
+
+
+def require_sm100(device):
+    if device.type != 'cuda':
+        raise ValueError('a CUDA device is required')
+    if torch.cuda.get_device_capability(device)[0] != 10:
+        raise RuntimeError('thunderworld_b200 kernels are built for sm_100a (B200) only; no fallback exists')
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device):
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+@dataclass
+class Packed:
+    """Quantized activation: the reference's (codes, scales, factor, mp) tuple plus the atom-layout
+    scales and alpha that the fused GEMM reads (reference: cutlass/packing.py CutlassPacked)."""
+    codes: torch.Tensor          # uint8 [planes, mp, k/2]
+    scales: torch.Tensor         # float8_e4m3fn [planes, mp, k/16]
+    factor: torch.Tensor         # float32 scalar
+    mp: int
+    scales_swz: torch.Tensor     # uint8 [planes, ceil(m/128)*128, k/16] atom layout
+    alpha: torch.Tensor          # float32 scalar = factor * wg (when wg was given)
+    mask: torch.Tensor           # bool [ceil(m/128), k/128] or None
+
+    @property
+    def native(self):
+        return self.codes, self.scales, self.factor, self.mp
+
+    def __iter__(self):          # unpack like the reference tuple
+        return iter(self.native)
+
+
+# One scratch buffer per device and kernel family, shared by every call: like the reference engine,
+# callers issue one request at a time on one stream (docs/INFERENCE.md:51 of the reference).
+_workspaces = {}
+
+
+def _workspace(device, nbytes, key):
+    ws = _workspaces.get((device, key))
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 256), device=device, dtype=torch.uint8)
+        _workspaces[(device, key)] = ws
+    return ws
+
+
+def quantize(x, prescale=None, *, repair=1, mask=None, na=0, sensitivity=None, factor=None, wg=None,
+             base=1., res=1., gain=1., energy=1., workspace=None, out=None):
+    """bf16 [m,k] -> Packed. repair: 0 base only, 1 full residual, 2 residual under `mask`,
+    3 online selection of `na` K128 blocks per M128 row block (mask is written)."""
+    if x.ndim != 2 or x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError('expected contiguous BF16 [M,K]')
+    require_sm100(x.device)
+    m, k = x.shape
+    if m == 0:
+        raise ValueError('empty activation rows are unsupported')
+    if k % 128:
+        raise ValueError('K must be a multiple of 128')
+    lib = _lib.load()
+    mp = cdiv(m, 16) * 16
+    mb = cdiv(m, 128)
+    planes = 2 if repair else 1
+    dev = x.device
+    if out is None:
+        codes = torch.empty((planes, mp, k // 2), device=dev, dtype=torch.uint8)
+        scales = torch.empty((planes, mp, k // 16), device=dev, dtype=torch.float8_e4m3fn)
+        swz = torch.empty((planes, mb * 128, k // 16), device=dev, dtype=torch.uint8)
+        fac = torch.empty((), device=dev, dtype=torch.float32) if factor is None else factor
+        alpha = torch.empty((), device=dev, dtype=torch.float32)
+        if repair == 3 and mask is None:
+            mask = torch.empty((mb, k // 128), device=dev, dtype=torch.bool)
+    else:
+        codes, scales, swz, fac, alpha = out.codes, out.scales, out.scales_swz, out.factor, out.alpha
+        mask = out.mask if mask is None else mask
+    if repair in (2, 3) and (mask is None or mask.dtype != torch.bool or tuple(mask.shape) != (mb, k // 128)
+                             or not mask.is_contiguous()):
+        raise ValueError(f'mask must be contiguous bool {(mb, k // 128)}')
+    if workspace is None:
+        workspace = _workspace(dev, lib.tw_quantize_workspace(m, k), 'q')
+    args = _lib.QuantizeArgs(_ptr(x), _ptr(prescale), _ptr(sensitivity), _ptr(fac), _ptr(wg), _ptr(alpha),
+                             _ptr(codes), _ptr(scales), _ptr(swz), _ptr(mask), _ptr(workspace),
+                             m, k, mp, int(repair), int(na), int(factor is not None),
+                             float(base), float(res), float(gain), float(energy))
+    with torch.cuda.device(dev):
+        _lib.check(lib.tw_quantize(ctypes.byref(args), _stream(dev)))
+    return Packed(codes, scales, fac, mp, swz, alpha, mask)
+
+
+def swizzle(scales):
+    """Row-major E4M3 [rows, cols] -> atom layout uint8 [ceil(rows/128)*128, cols]."""
+    if scales.dtype not in (torch.float8_e4m3fn, torch.uint8) or not scales.is_contiguous() or scales.ndim != 2:
+        raise ValueError('Contiguous E4M3 scales required')
+    rows, cols = scales.shape
+    if cols % 4:
+        raise ValueError('Scale columns must be divisible by four')
+    require_sm100(scales.device)
+    out = torch.empty((cdiv(rows, 128) * 128, cols), device=scales.device, dtype=torch.uint8)
+    with torch.cuda.device(scales.device):
+        _lib.check(_lib.load().tw_swizzle_scales(scales.data_ptr(), rows, cols, out.data_ptr(), _stream(scales.device)))
+    return out
+
+
+def fused_gemm(m, n, k, packed, wc, ws_swz, alpha, *, na=0, mask=None, wr=None, wrs_swz=None, wi=None, off=None,
+               wloc=None, cross=False, shared=False, dense=False, ws=None, wrs=None, out=None, workspace=None):
+    """One launch of the repaired GEMM; returns bf16 [m,n]."""
+    lib = _lib.load()
+    dev = wc.device
+    require_sm100(dev)
+    if out is None:
+        out = torch.empty((m, n), device=dev, dtype=torch.bfloat16)
+    if workspace is None:
+        workspace = _workspace(dev, lib.tw_workspace(m, n, k), 'g')
+    hasw = wr is not None and wr.numel() > 0
+    a0s = packed.scales_swz[0]
+    a1s = packed.scales_swz[1] if packed.scales_swz.shape[0] > 1 else None
+    io = _lib.RepairIO(_ptr(packed.codes), _ptr(packed.scales), _ptr(wc), _ptr(ws), _ptr(wr) if hasw else None,
+                       _ptr(wrs) if hasw else None, _ptr(wi), _ptr(off), _ptr(wloc), _ptr(mask),
+                       m, packed.mp, n, k, int(na), int(hasw), int(cross), int(shared), int(dense),
+                       int(wr.shape[0]) if hasw else 0, _ptr(a1s) if na else None, _ptr(wrs_swz) if hasw else None)
+    with torch.cuda.device(dev):
+        _lib.check(lib.tw_fused(m, n, k, packed.codes.data_ptr(), wc.data_ptr(), a0s.data_ptr(), ws_swz.data_ptr(),
+                                out.data_ptr(), alpha.data_ptr(), workspace.data_ptr(), _stream(dev), ctypes.byref(io)))
+    return out
+
+
+def device_status(device=None):
+    """Read the status word the GEMM kernels write on a bounded-wait timeout (synchronises)."""
+    dev = torch.device('cuda', torch.cuda.current_device()) if device is None else device
+    ws = _workspaces.get((dev, 'g'))
+    return 0 if ws is None else int(ws[:4].view(torch.int32).item())
