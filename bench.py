@@ -1,0 +1,321 @@
+"""Benchmark of the selective-FP4-repair projection path.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--budget 2.0|1.5]
+
+One step = one pass over the Cosmos3-Edge-shaped projection set (M = 7680 tokens; QKV 6144x2048,
+out-proj 2048x2048, FFN-up 8192x2048, FFN-down 2048x8192): for every projection the online
+activation quantizer with A1 block selection, then the fused repair GEMM with the seeded W1 tile
+plan of the chosen issued-work budget (FFN-down with the A1W1 cross term). The reported metric is
+effective TFLOP/s on issued FP4 work (2*M*N*K-scaled, padding excluded) over all ranks.
+
+N > 1: data-parallel replicas of the same projection set (one process per GPU, no data-path
+collective), weak scaling. The tensor-parallel step benchmark lives in the package's DiT runner.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M_TOKENS = 7680
+PROJECTIONS = (('qkv', 6144, 2048), ('out', 2048, 2048), ('ffn_up', 8192, 2048), ('ffn_down', 2048, 8192))
+NOMINAL_FP4_TFLOPS = 9000.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one fused_kernel<256> launch (qkv, 2x plan), from the
+# ncu capture summarised under profiles/; None until a capture exists.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def plan_for(name, n, k, budget, seed):
+    """Issued-work plan of one layer: A quota, W1 tile ids, cross. 1.5x: a = KB/4 and 25 % of the
+    W tiles; 2x: a = KB/2 and 50 %. FFN-down adds the cross term and trims W tiles (highest ids
+    first) until the provable bound 1 + a/KB + w/(NB*KB) + cross_bound <= budget holds."""
+    kb, nb = k // 128, n // 128
+    frac = 0.25 if budget < 1.75 else 0.5
+    na = int(kb * frac)
+    rng = np.random.default_rng(seed + 7919)
+    tiles = sorted(int(t) for t in rng.permutation(nb * kb)[:int(round(frac * nb * kb))])
+    cross = name == 'ffn_down'
+    if cross:
+        def ratio(ts):
+            counts = np.bincount(np.array(ts, dtype=np.int64) % kb, minlength=kb) if ts else np.zeros(kb, int)
+            bound = int(np.sort(counts)[::-1][:na].sum())
+            return 1 + na / kb + len(ts) / (nb * kb) + bound / (nb * kb)
+        while tiles and ratio(tiles) > budget:
+            tiles = tiles[:-1]
+    return na, tiles, cross
+
+
+class Layer:
+    """One projection: offline weights + plan + preallocated activation."""
+
+    def __init__(self, name, n, k, m, budget, seed, device):
+        import torch
+        from thunderworld_b200.native import Native, quantize_weight
+        self.name, self.n, self.k, self.m = name, n, k, m
+        self.na, self.tiles, self.cross = plan_for(name, n, k, budget, seed)
+        kb, nb, mb = k // 128, n // 128, (m + 127) // 128
+        gen = torch.Generator(device='cpu').manual_seed(seed)
+        x = torch.randn(m, k, generator=gen)
+        cols = torch.randperm(k, generator=gen)[:max(1, round(0.005 * k))]
+        x[:, cols] *= 20
+        self.x_host = x.bfloat16().pin_memory()
+        self.x = self.x_host.to(device, non_blocking=True)
+        w = (torch.randn(n, k, generator=gen) * 0.02).bfloat16().to(device)
+        wc, ws, wg = quantize_weight(w)
+        am = torch.zeros(mb, kb, dtype=torch.bool); am[:, :self.na] = True       # placeholder support, rewritten online
+        wm = torch.zeros(nb * kb, dtype=torch.bool); wm[self.tiles] = True
+        self.op = Native(wc, ws, wg, torch.ones(k, device=device), am.repeat_interleave(128, 1).to(device),
+                         wm.reshape(nb, kb).repeat_interleave(128, 0).repeat_interleave(128, 1).to(device),
+                         cross=self.cross)
+        self.sens = (w.float() ** 2).sum(0).contiguous()                          # selector weights: sum_n W^2
+        self.out = torch.empty(m, n, device=device, dtype=torch.bfloat16)
+        self.out_host = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
+        self.packed = None
+        del w
+
+    def quantize(self, x):
+        from thunderworld_b200 import ops
+        self.packed = ops.quantize(x, None, repair=3, na=self.na, sensitivity=self.sens, mask=self.op.am,
+                                   wg=self.op.wg, out=self.packed)
+        return self.packed
+
+    def gemm(self, x):
+        return self.op.run_packed(x, self.packed, out=self.out)
+
+    def issued_flops(self):
+        """Issued FP4 FLOPs with the realised A support (M is a multiple of 128: no padding)."""
+        from thunderworld_b200.cosmos.budget import linear_cost
+        support = [row.nonzero().flatten().tolist() for row in self.op.am.cpu()]
+        return linear_cost(self.m, self.n, self.k, a_blocks=self.na, w_blocks=self.tiles, cross=self.cross,
+                           a_support=support)['total_mma']
+
+
+class ClockSampler(threading.Thread):
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.stop_flag = index, [], set(), False
+        self.max_mhz = None
+
+    def run(self):
+        fields = ('clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+                  'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+        names = ('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap')
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(['nvidia-smi', f'--query-gpu={fields}', '--format=csv,noheader,nounits', '-i',
+                                      str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
+                parts = [p.strip() for p in out.split(',')]
+                self.samples.append(float(parts[0])); self.max_mhz = float(parts[1])
+                for name, val in zip(names, parts[2:]):
+                    if val.lower().startswith('active'):
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.05)
+
+    def result(self):
+        return {'sm_mhz': float(np.median(self.samples)) if self.samples else None, 'sm_max_mhz': self.max_mhz,
+                'reasons': sorted(self.reasons), 'samples': len(self.samples)}
+
+
+def cpu_baseline(budget, threads, sample_rows=1536):
+    """The oracle's emulation of the same path on host cores: numpy quantizer + decoded fp32
+    matmuls per term, on a bounded sample (the first `sample_rows` rows of the QKV projection)."""
+    from oracle import nvfp4_oracle as o
+    name, n, k = PROJECTIONS[0]
+    na, tiles, cross = plan_for(name, n, k, budget, 0)
+    x = o.synthetic_activation(sample_rows, k, 0)
+    w = o.synthetic_weight(n, k, 0)
+    wc, wsb, wf = o.quantize_weight(w)
+    sens = (w.astype(np.float64) ** 2).sum(0).astype(np.float32)
+    t0 = time.perf_counter()
+    ac, asb, af = o.quantize_linear_input(x, rows_padded=sample_rows)
+    scores, _ = o.residual_scores(x, None, sens)
+    mask = o.choose_blocks(scores, na)
+    o.repair_linear(ac, asb, af, wc, wsb, wf, sample_rows, a_mask=mask, w_tiles=tiles, cross=cross)
+    dt = time.perf_counter() - t0
+    flops = o.issued_flops(sample_rows, n, k, a_mask=mask, w_tiles=tiles, cross=cross)
+    return flops / dt / 1e12, dt, f'{sample_rows} rows of the qkv projection ({n}x{k}), quantize+select+{3 + cross}-term decoded matmul'
+
+
+def run_reference(args):
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    for _ in range(args.warmup):
+        cpu_baseline(args.budget, threads, 256)
+    vals, times = [], []
+    for _ in range(args.steps):
+        v, dt, sample = cpu_baseline(args.budget, threads)
+        vals.append(v); times.append(dt)
+    value = float(np.mean(vals))
+    line = {'metric': 'repaired NVFP4 GEMM effective TFLOPS on issued FP4 work', 'impl': 'reference', 'value': value,
+            'unit': 'TFLOP/s', 'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup,
+            'ms_per_step': float(np.mean(times)) * 1e3, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+            'dtype': 'nvfp4 (e2m1 x ue4m3, fp32 accumulate)', 'data': 'synthetic',
+            'config': workload_config(args.budget, 1),
+            'cpu_baseline': {'value': value, 'unit': 'TFLOP/s', 'cores': threads, 'kind': 'port', 'sample': sample},
+            'e2e': {'value': value, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}
+    print(json.dumps(line))
+
+
+def workload_config(budget, world, m=M_TOKENS, layers='qkv,out,ffn_up,ffn_down'):
+    return {'workload': f'cosmos3-edge projection set (config 1), M={m}, layers {layers}, '
+                        f'{budget}x issued-work plan, cross term on FFN-down',
+            'budget': budget, 'replicas': world, 'parallelism': f'dp{world}',
+            'l2': 'per-step working set ~0.55 GB (activations, packed planes, outputs) exceeds the 126 MB L2'}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--impl', default='ours')
+    ap.add_argument('--budget', type=float, default=2.0)
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer timing (profiling runs)')
+    ap.add_argument('--m-tokens', type=int, default=M_TOKENS, help='rows per projection (smaller for profiler captures)')
+    ap.add_argument('--layers', default='qkv,out,ffn_up,ffn_down', help='subset of the projection set')
+    args = ap.parse_args()
+    if args.impl == 'reference':
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    if not torch.cuda.is_available():
+        raise RuntimeError('bench.py needs a CUDA device: the product path has no CPU fallback')
+    torch.cuda.set_device(local)
+    device = torch.device('cuda', local)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=device)
+    from thunderworld_b200 import ops
+
+    chosen = args.layers.split(',')
+    layers = [Layer(name, n, k, args.m_tokens, args.budget, seed, device)
+              for seed, (name, n, k) in enumerate(PROJECTIONS) if name in chosen]
+    torch.cuda.synchronize()
+    stream = torch.cuda.current_stream()
+
+    def step():
+        for layer in layers:
+            layer.quantize(layer.x)
+            layer.gemm(layer.x)
+
+    def step_e2e():
+        for layer in layers:
+            layer.x.copy_(layer.x_host, non_blocking=True)
+            layer.quantize(layer.x)
+            layer.gemm(layer.x)
+            layer.out_host.copy_(layer.out, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    flops_step = sum(layer.issued_flops() for layer in layers)
+
+    # device-resident timing, with per-launch events around the dominant kernel
+    sampler = ClockSampler(local)
+    sampler.start()
+    gemm_events = []
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record(stream)
+    for _ in range(args.steps):
+        for layer in layers:
+            layer.quantize(layer.x)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            layer.gemm(layer.x)
+            e1.record(stream)
+            gemm_events.append((layer.name, e0, e1))
+    t1.record(stream)
+    barrier()
+    sampler.stop_flag = True
+    ms = t0.elapsed_time(t1)
+    if ops.device_status(device) != 0:
+        raise RuntimeError('device status word reports a bounded-wait timeout')
+
+    # end to end: pinned host inputs in, outputs back to pinned host memory, every step
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(0 if args.no_e2e else 2):
+        step_e2e()
+    barrier()
+    s0.record(stream)
+    for _ in range(0 if args.no_e2e else args.steps):
+        step_e2e()
+    s1.record(stream)
+    barrier()
+    ms_e2e = max(s0.elapsed_time(s1), 1e-9)
+
+    times = torch.tensor([ms, ms_e2e], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = float(times[0]), float(times[1])
+    sampler.join(timeout=2)
+
+    per_layer = {}
+    for name, e0, e1 in gemm_events:
+        per_layer.setdefault(name, []).append(e0.elapsed_time(e1))
+    flops_by_layer = {layer.name: layer.issued_flops() for layer in layers}
+    gemm_ms = sum(sum(v) for v in per_layer.values())
+    gemm_launches = sum(len(v) for v in per_layer.values())
+    achieved = sum(flops_by_layer[n_] * len(v) for n_, v in per_layer.items()) / (gemm_ms * 1e-3) / 1e12
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, 'MEASURED_PEAKS.json')))
+    except Exception:
+        pass
+
+    if rank == 0:
+        value = world * flops_step * args.steps / (ms * 1e-3) / 1e12
+        e2e = world * flops_step * args.steps / (ms_e2e * 1e-3) / 1e12
+        h2d = sum(l.x_host.numel() * 2 for l in layers)
+        d2h = sum(l.out_host.numel() * 2 for l in layers)
+        line = {
+            'metric': 'repaired NVFP4 GEMM effective TFLOPS on issued FP4 work', 'value': value, 'unit': 'TFLOP/s',
+            'n_gpus': world, 'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms / args.steps,
+            'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+            'dtype': 'nvfp4 (e2m1 x ue4m3, fp32 accumulate)', 'data': 'synthetic',
+            'config': workload_config(args.budget, world, args.m_tokens, args.layers),
+            'e2e': {'value': e2e, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
+                    'ms_per_step': ms_e2e / args.steps},
+            'gpu_launches': args.steps * len(layers) * 4,
+            'clocks': sampler.result(),
+            'roofline': {'bound': 'tensor', 'kernel': 'fused_kernel (tcgen05 mxf4nvf4 repair GEMM)',
+                         'achieved': achieved, 'peak': NOMINAL_FP4_TFLOPS, 'unit': 'TFLOP/s',
+                         'frac': achieved / NOMINAL_FP4_TFLOPS,
+                         'peak_source': 'nominal dense FP4 (MEASURED_PEAKS.json holds no FP4 figure)',
+                         'frac_of_4x_measured_bf16': achieved / (4 * peaks['bf16_tflops_sustained']) if peaks else None,
+                         'traffic': NCU_TRAFFIC_BYTES_PER_LAUNCH, 'launches': gemm_launches,
+                         'avg_launch_ms': gemm_ms / gemm_launches,
+                         'per_layer_tflops': {n_: flops_by_layer[n_] / (np.mean(v) * 1e-3) / 1e12 for n_, v in per_layer.items()},
+                         'gemm_share_of_step': gemm_ms / ms},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            v, dt, sample = cpu_baseline(args.budget, os.cpu_count() or 1)
+            line['cpu_baseline'] = {'value': v, 'unit': 'TFLOP/s', 'cores': os.cpu_count() or 1, 'kind': 'port',
+                                    'sample': sample, 'seconds': dt}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()
