@@ -37,6 +37,8 @@ def plan_for(name, n, k, budget, seed):
     W tiles; 2x: a = KB/2 and 50 %. FFN-down adds the cross term and trims W tiles (highest ids
     first) until the provable bound 1 + a/KB + w/(NB*KB) + cross_bound <= budget holds."""
     kb, nb = k // 128, n // 128
+    if budget <= 1.0:                     # base W4A4: no repair term
+        return 0, [], False
     frac = 0.25 if budget < 1.75 else 0.5
     na = int(kb * frac)
     rng = np.random.default_rng(seed + 7919)
@@ -82,8 +84,11 @@ class Layer:
 
     def quantize(self, x):
         from thunderworld_b200 import ops
-        self.packed = ops.quantize(x, None, repair=3, na=self.na, sensitivity=self.sens, mask=self.op.am,
-                                   wg=self.op.wg, out=self.packed)
+        if self.na == 0:
+            self.packed = ops.quantize(x, None, repair=0, wg=self.op.wg, out=self.packed)
+        else:
+            self.packed = ops.quantize(x, None, repair=3, na=self.na, sensitivity=self.sens, mask=self.op.am,
+                                       wg=self.op.wg, out=self.packed)
         return self.packed
 
     def gemm(self, x):

@@ -13,41 +13,44 @@
 // CTA = one 128 x BN output tile at a time (persistent over tiles), warp-specialised:
 //   warp 0      producer: TMA loads of code tiles (64-byte swizzle) + bulk copies of scale atoms
 //   warp 1      MMA issuer: scale atoms smem -> TMEM (tcgen05.cp), MMAs, commits
-//   warps 2..   epilogue: TMEM -> registers -> bf16 -> swizzled smem -> TMA store
-// Operand rings: "A" slots (128 rows x 64 B codes + 1 KB scales) and "B" slots (BN rows x 64 B
-// codes + BN/128 KB scales); W1 tiles (128 rows) use a B slot. No cluster, no multicast.
+//   warp 2      builds the per-tile term tables (A-support bytes, W1 bank positions) ahead of use
+//   warps 4-11  epilogue: TMEM -> registers -> bf16 -> global (16-byte stores), TMEM released first
+// Operand rings: A slots (128 rows x 64 B codes + 1 KB scales), W0 slots (BN rows x 64 B codes +
+// BN/128 KB scales) and W1 slots (128 rows). No cluster, no multicast.
 #include <cuda.h>
 #include "tw_common.cuh"
 #include "../../include/twb200.h"
 
 namespace {
 
-constexpr int KB_MAX = 512;               // K <= 65536
+constexpr int KB_MAX = 256;               // K <= 32768
 constexpr int A_TILE = 128 * 64;          // bytes of one 128 x K128 code tile
 constexpr int SF_ATOM = 1024;             // bytes of the scales of 128 rows x K128
 
 template <int BN> struct Cfg {
   static constexpr int HALVES = BN / 128;
-  static constexpr int A_SLOTS = 6;
-  static constexpr int B_SLOTS = BN == 256 ? 5 : 8;
+  static constexpr int A_SLOTS = 7;                           // A0 / A1 tiles
+  static constexpr int B_SLOTS = BN == 256 ? 6 : 8;           // W0 tiles (BN rows)
+  static constexpr int W_SLOTS = 4;                           // W1 tiles (128 rows)
+  static constexpr int TAB_SLOTS = 3;                         // per-tile term tables built ahead
   static constexpr int ACC_STAGES = BN == 256 ? 1 : 2;
   static constexpr int EPI_WARPS = 8;
+  static constexpr int FIRST_EPI_WARP = 4;                    // warps 0..3: producer, MMA, tables, spare
   static constexpr int EPI_GROUPS = EPI_WARPS / 4;            // column groups per lane quadrant
   static constexpr int EPI_COLS = BN / EPI_GROUPS;            // columns per epilogue warp
-  static constexpr int EPI_CHUNKS = EPI_COLS / 64;            // 64-column (128-byte) store chunks
-  static constexpr int THREADS = (2 + EPI_WARPS) * 32;
+  static constexpr int THREADS = (FIRST_EPI_WARP + EPI_WARPS) * 32;
   static constexpr int B_TILE = BN * 64;
-  static constexpr int STAGE_BYTES = 32 * 128;                // one warp's 32 rows x 64 bf16
   // shared-memory carve-up (offsets from a 1024-aligned base)
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + A_SLOTS * A_TILE;
-  static constexpr int OFF_OUT = OFF_B + B_SLOTS * B_TILE;
-  static constexpr int OFF_SFA = OFF_OUT + EPI_WARPS * EPI_CHUNKS * STAGE_BYTES;
+  static constexpr int OFF_W = OFF_B + B_SLOTS * B_TILE;
+  static constexpr int OFF_SFA = OFF_W + W_SLOTS * A_TILE;
   static constexpr int OFF_SFB = OFF_SFA + A_SLOTS * SF_ATOM;
-  static constexpr int OFF_TAB = OFF_SFB + B_SLOTS * HALVES * SF_ATOM;
-  static constexpr int TAB_BYTES = 2 * (HALVES * KB_MAX * 4 + KB_MAX);   // producer copy + MMA copy
-  static constexpr int OFF_BAR = OFF_TAB + TAB_BYTES;
-  static constexpr int NUM_BARS = 2 * A_SLOTS + 2 * B_SLOTS + 2 * ACC_STAGES;
+  static constexpr int OFF_SFW = OFF_SFB + B_SLOTS * HALVES * SF_ATOM;
+  static constexpr int OFF_TAB = OFF_SFW + W_SLOTS * SF_ATOM;
+  static constexpr int TAB_BYTES = HALVES * KB_MAX * 4 + KB_MAX;
+  static constexpr int OFF_BAR = OFF_TAB + TAB_SLOTS * TAB_BYTES;
+  static constexpr int NUM_BARS = 2 * A_SLOTS + 2 * B_SLOTS + 2 * W_SLOTS + 2 * TAB_SLOTS + 2 * ACC_STAGES;
   static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 64 + 1024;  // + alignment slack
   // tensor-memory columns
   static constexpr int TM_ACC = 0;
@@ -55,6 +58,7 @@ template <int BN> struct Cfg {
   static constexpr int TM_SFA0 = TM_SF, TM_SFA1 = TM_SF + 16, TM_SFB0 = TM_SF + 32, TM_SFBW = TM_SF + 32 + 2 * 4 * HALVES * 2;
   static constexpr int TM_COLS = 512;
 };
+static_assert(Cfg<256>::SMEM_BYTES <= 232448 && Cfg<128>::SMEM_BYTES <= 232448, "shared memory budget");
 
 struct Params {
   const uint8_t* sfa0;      // atom-layout scales of A0  [MB*128, K/16]
@@ -64,6 +68,7 @@ struct Params {
   const int* wi; const int* off; const int* wloc;
   const uint8_t* mask;
   const float* alpha;
+  __nv_bfloat16* out;
   int* status;
   int m, mp, n, k, na, hasw, cross, shared, dense;
   int kb, nb, mb, tiles_n, tiles;
@@ -79,61 +84,70 @@ template <int BN> struct TermTable {
 template <int BN>
 __device__ __forceinline__ void build_table(TermTable<BN>& tab, const Params& p, int mbi, int nt, int lane) {
   constexpr int H = Cfg<BN>::HALVES;
+  int begin[H], end[H];
+#pragma unroll
+  for (int h = 0; h < H; ++h) {
+    const int nb = nt * H + h;
+    const bool use = p.hasw && !p.dense && nb < p.nb;
+    begin[h] = use ? p.off[nb] : 0;
+    end[h] = use ? p.off[nb + 1] : 0;
+  }
   for (int kb = lane; kb < p.kb; kb += 32) {
     tab.a1[kb] = p.na == p.kb ? 1 : (p.na > 0 ? p.mask[mbi * p.kb + kb] : 0);
 #pragma unroll
     for (int h = 0; h < H; ++h) {
-      int nb = nt * H + h;
+      const int nb = nt * H + h;
       tab.w1[h][kb] = (p.hasw && p.dense && nb < p.nb) ? nb * p.kb + kb : -1;
     }
   }
   __syncwarp();
-  if (p.hasw && !p.dense) {
 #pragma unroll
-    for (int h = 0; h < H; ++h) {
-      int nb = nt * H + h;
-      if (nb < p.nb) {
-        int begin = p.off[nb], end = p.off[nb + 1];
-        for (int s = begin + lane; s < end; s += 32) tab.w1[h][p.wi[s]] = p.shared ? p.wloc[s] : s;
-      }
-    }
-  }
+  for (int h = 0; h < H; ++h)
+    for (int s = begin[h] + lane; s < end[h]; s += 32) tab.w1[h][p.wi[s]] = p.shared ? p.wloc[s] : s;
   __syncwarp();
 }
 
 template <int BN>
 __global__ void __launch_bounds__(Cfg<BN>::THREADS, 1)
 fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w0,
-             const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__ CUtensorMap tm_out, const Params p) {
+             const __grid_constant__ CUtensorMap tm_w1, const Params p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem + C::OFF_A;
   uint8_t* sB = smem + C::OFF_B;
-  uint8_t* sOut = smem + C::OFF_OUT;
+  uint8_t* sW = smem + C::OFF_W;
   uint8_t* sSFA = smem + C::OFF_SFA;
   uint8_t* sSFB = smem + C::OFF_SFB;
-  TermTable<BN>* tabs = reinterpret_cast<TermTable<BN>*>(smem + C::OFF_TAB);
+  uint8_t* sSFW = smem + C::OFF_SFW;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint64_t* fullA = bars;
   uint64_t* emptyA = fullA + C::A_SLOTS;
   uint64_t* fullB = emptyA + C::A_SLOTS;
   uint64_t* emptyB = fullB + C::B_SLOTS;
-  uint64_t* accFull = emptyB + C::B_SLOTS;
+  uint64_t* fullW = emptyB + C::B_SLOTS;
+  uint64_t* emptyW = fullW + C::W_SLOTS;
+  uint64_t* tabFull = emptyW + C::W_SLOTS;
+  uint64_t* tabEmpty = tabFull + C::TAB_SLOTS;
+  uint64_t* accFull = tabEmpty + C::TAB_SLOTS;
   uint64_t* accEmpty = accFull + C::ACC_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accEmpty + C::ACC_STAGES);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  auto table = [&](uint32_t i) -> TermTable<BN>& {
+    return *reinterpret_cast<TermTable<BN>*>(smem + C::OFF_TAB + (i % C::TAB_SLOTS) * C::TAB_BYTES);
+  };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::A_SLOTS; ++i) { tw::mbar_init(fullA + i, 1); tw::mbar_init(emptyA + i, 1); }
     for (int i = 0; i < C::B_SLOTS; ++i) { tw::mbar_init(fullB + i, 1); tw::mbar_init(emptyB + i, 1); }
+    for (int i = 0; i < C::W_SLOTS; ++i) { tw::mbar_init(fullW + i, 1); tw::mbar_init(emptyW + i, 1); }
+    for (int i = 0; i < C::TAB_SLOTS; ++i) { tw::mbar_init(tabFull + i, 1); tw::mbar_init(tabEmpty + i, 2); }
     for (int i = 0; i < C::ACC_STAGES; ++i) { tw::mbar_init(accFull + i, 1); tw::mbar_init(accEmpty + i, C::EPI_WARPS); }
     *abort_flag = 0;
     tw::fence_barrier_init();
-    tw::tma_prefetch_desc(&tm_a); tw::tma_prefetch_desc(&tm_w0);
-    tw::tma_prefetch_desc(&tm_w1); tw::tma_prefetch_desc(&tm_out);
+    tw::tma_prefetch_desc(&tm_a); tw::tma_prefetch_desc(&tm_w0); tw::tma_prefetch_desc(&tm_w1);
   }
   if (warp == 1) { tw::tmem_alloc(tmem_slot, C::TM_COLS); tw::tmem_relinquish(); }
   tw::tc_fence_before();
@@ -141,16 +155,26 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   tw::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ producer
-    TermTable<BN>& tab = tabs[0];
-    uint32_t ia = 0, ib = 0;                       // running slot counters
+  if (warp == 2) {
+    // ------------------------------------------------------------------ term tables, built ahead
+    uint32_t it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x) {
-      const int mbi = tile / p.tiles_n, nt = tile % p.tiles_n;
-      __syncwarp();
-      build_table<BN>(tab, p, mbi, nt, lane);
-      if (lane == 0) {
+    for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
+      ok = tw::mbar_wait(tabEmpty + it % C::TAB_SLOTS, ((it / C::TAB_SLOTS) & 1) ^ 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      build_table<BN>(table(it), p, tile / p.tiles_n, tile % p.tiles_n, lane);
+      if (lane == 0) tw::mbar_arrive(tabFull + it % C::TAB_SLOTS);
+    }
+  } else if (warp == 0) {
+    // ------------------------------------------------------------------ producer (one thread)
+    if (lane == 0) {
+      uint32_t ia = 0, ib = 0, iw = 0, it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
+        const int mbi = tile / p.tiles_n, nt = tile % p.tiles_n;
+        const TermTable<BN>& tab = table(it);
+        ok = tw::mbar_wait(tabFull + it % C::TAB_SLOTS, (it / C::TAB_SLOTS) & 1, abort_flag);
         const int n_rows = min(BN, p.n - nt * BN);            // 128 or BN
         for (int kb = 0; kb < p.kb && ok; ++kb) {
           const bool sel = tab.a1[kb] != 0;
@@ -180,33 +204,36 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
           for (int h = 0; h < C::HALVES && ok; ++h) {
             const int loc = tab.w1[h][kb];
             if (loc < 0) continue;
-            const uint32_t s = ib % C::B_SLOTS, ph = (ib / C::B_SLOTS) & 1; ++ib;
-            ok = tw::mbar_wait(emptyB + s, ph ^ 1, abort_flag);
+            const uint32_t s = iw % C::W_SLOTS, ph = (iw / C::W_SLOTS) & 1; ++iw;
+            ok = tw::mbar_wait(emptyW + s, ph ^ 1, abort_flag);
             if (!ok) break;
-            tw::mbar_expect_tx(fullB + s, A_TILE + SF_ATOM);
-            tw::tma_load_2d(sB + s * C::B_TILE, &tm_w1, 0, loc * 128, fullB + s);
-            tw::bulk_load(sSFB + s * C::HALVES * SF_ATOM, p.sfbw + (size_t)loc * SF_ATOM, SF_ATOM, fullB + s);
+            tw::mbar_expect_tx(fullW + s, A_TILE + SF_ATOM);
+            tw::tma_load_2d(sW + s * A_TILE, &tm_w1, 0, loc * 128, fullW + s);
+            tw::bulk_load(sSFW + s * SF_ATOM, p.sfbw + (size_t)loc * SF_ATOM, SF_ATOM, fullW + s);
           }
         }
+        tw::mbar_arrive(tabEmpty + it % C::TAB_SLOTS);
       }
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    TermTable<BN>& tab = tabs[1];
-    uint32_t ia = 0, ib = 0, it = 0, iw = 0;
-    bool ok = true;
-    constexpr uint32_t IDESC_FULL = tw::make_idesc_nvf4(128, BN);
-    constexpr uint32_t IDESC_128 = tw::make_idesc_nvf4(128, 128);
-    for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
-      const int mbi = tile / p.tiles_n, nt = tile % p.tiles_n;
-      __syncwarp();
-      build_table<BN>(tab, p, mbi, nt, lane);
-      if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (one thread)
+    if (lane == 0) {
+      uint32_t ia = 0, ib = 0, iw = 0, it = 0;
+      bool ok = true;
+      constexpr uint32_t IDESC_FULL = tw::make_idesc_nvf4(128, BN);
+      constexpr uint32_t IDESC_128 = tw::make_idesc_nvf4(128, 128);
+      const uint64_t desc_hi = tw::make_smem_desc(0, 16, 512, 4);   // 64-byte swizzle, 8-row groups 512 B apart
+      const uint64_t sf_hi = tw::make_smem_desc(0, 0, 128, 0);      // scale atom: 32 rows x 16 B, no swizzle
+      auto op_desc = [&](uint32_t addr) { return desc_hi | (uint64_t)((addr >> 4) & 0x3fffu); };
+      auto sf_desc = [&](uint32_t addr) { return sf_hi | (uint64_t)((addr >> 4) & 0x3fffu); };
+      for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
+        const int nt = tile % p.tiles_n;
+        const TermTable<BN>& tab = table(it);
+        ok = tw::mbar_wait(tabFull + it % C::TAB_SLOTS, (it / C::TAB_SLOTS) & 1, abort_flag);
         const int n_rows = min(BN, p.n - nt * BN);
         const uint32_t idesc_base = n_rows == BN ? IDESC_FULL : IDESC_128;
         const uint32_t stage = it % C::ACC_STAGES, aph = (it / C::ACC_STAGES) & 1;
-        ok = tw::mbar_wait(accEmpty + stage, aph ^ 1, abort_flag);
+        ok = ok && tw::mbar_wait(accEmpty + stage, aph ^ 1, abort_flag);
         tw::tc_fence_after();
         const uint32_t acc = tmem + C::TM_ACC + stage * BN;
         for (int kb = 0; kb < p.kb && ok; ++kb) {
@@ -221,19 +248,19 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
           if (!ok) break;
           tw::tc_fence_after();
           const uint32_t a0_addr = tw::smem_u32(sA + sa0 * A_TILE), b0_addr = tw::smem_u32(sB + sb0 * C::B_TILE);
+          const uint32_t sfa0_addr = tw::smem_u32(sSFA + sa0 * SF_ATOM), sfb0_addr = tw::smem_u32(sSFB + sb0 * C::HALVES * SF_ATOM);
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
-            tw::tc_copy_scales(t_sfa0 + 4 * c, tw::make_smem_desc(tw::smem_u32(sSFA + sa0 * SF_ATOM + c * 512), 0, 128, 0));
+            tw::tc_copy_scales(t_sfa0 + 4 * c, sf_desc(sfa0_addr + c * 512));
 #pragma unroll
             for (int h = 0; h < C::HALVES; ++h)
               if (h * 128 < n_rows)
-                tw::tc_copy_scales(t_sfb0 + 4 * C::HALVES * c + 4 * h,
-                                   tw::make_smem_desc(tw::smem_u32(sSFB + (sb0 * C::HALVES + h) * SF_ATOM + c * 512), 0, 128, 0));
+                tw::tc_copy_scales(t_sfb0 + 4 * C::HALVES * c + 4 * h, sf_desc(sfb0_addr + h * SF_ATOM + c * 512));
           }
 #pragma unroll
           for (int c = 0; c < 2; ++c)
-            tw::tc_mma_nvf4(acc, tw::make_smem_desc(a0_addr + 32 * c, 16, 512, 4), tw::make_smem_desc(b0_addr + 32 * c, 16, 512, 4),
-                            idesc_base, t_sfa0 + 4 * c, t_sfb0 + 4 * C::HALVES * c, (kb | c) != 0);
+            tw::tc_mma_nvf4(acc, op_desc(a0_addr + 32 * c), op_desc(b0_addr + 32 * c), idesc_base, t_sfa0 + 4 * c,
+                            t_sfb0 + 4 * C::HALVES * c, (kb | c) != 0);
           // A1 against the same W0 tile
           uint32_t sa1 = 0, a1_addr = 0;
           if (sel) {
@@ -242,105 +269,86 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
             if (!ok) break;
             tw::tc_fence_after();
             a1_addr = tw::smem_u32(sA + sa1 * A_TILE);
+            const uint32_t sfa1_addr = tw::smem_u32(sSFA + sa1 * SF_ATOM);
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tw::tc_copy_scales(t_sfa1 + 4 * c, sf_desc(sfa1_addr + c * 512));
 #pragma unroll
             for (int c = 0; c < 2; ++c)
-              tw::tc_copy_scales(t_sfa1 + 4 * c, tw::make_smem_desc(tw::smem_u32(sSFA + sa1 * SF_ATOM + c * 512), 0, 128, 0));
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
-              tw::tc_mma_nvf4(acc, tw::make_smem_desc(a1_addr + 32 * c, 16, 512, 4), tw::make_smem_desc(b0_addr + 32 * c, 16, 512, 4),
-                              idesc_base, t_sfa1 + 4 * c, t_sfb0 + 4 * C::HALVES * c, 1u);
+              tw::tc_mma_nvf4(acc, op_desc(a1_addr + 32 * c), op_desc(b0_addr + 32 * c), idesc_base, t_sfa1 + 4 * c,
+                              t_sfb0 + 4 * C::HALVES * c, 1u);
           }
           tw::tc_commit(emptyB + sb0);
           // W1 tiles of this kb: 128-column MMAs into the matching half of the accumulator
           for (int h = 0; h < C::HALVES && ok; ++h) {
             if (tab.w1[h][kb] < 0) continue;
-            const uint32_t sbw = ib % C::B_SLOTS, pbw = (ib / C::B_SLOTS) & 1; ++ib;
-            ok = tw::mbar_wait(fullB + sbw, pbw, abort_flag);
+            const uint32_t sw = iw % C::W_SLOTS, pw = (iw / C::W_SLOTS) & 1;
+            const uint32_t t_sfbw = tmem + C::TM_SFBW + ((iw & 1) * 8);
+            ++iw;
+            ok = tw::mbar_wait(fullW + sw, pw, abort_flag);
             if (!ok) break;
             tw::tc_fence_after();
-            const uint32_t t_sfbw = tmem + C::TM_SFBW + ((iw++ & 1) * 8);
-            const uint32_t bw_addr = tw::smem_u32(sB + sbw * C::B_TILE);
+            const uint32_t bw_addr = tw::smem_u32(sW + sw * A_TILE), sfw_addr = tw::smem_u32(sSFW + sw * SF_ATOM);
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tw::tc_copy_scales(t_sfbw + 4 * c, sf_desc(sfw_addr + c * 512));
 #pragma unroll
             for (int c = 0; c < 2; ++c)
-              tw::tc_copy_scales(t_sfbw + 4 * c, tw::make_smem_desc(tw::smem_u32(sSFB + sbw * C::HALVES * SF_ATOM + c * 512), 0, 128, 0));
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
-              tw::tc_mma_nvf4(acc + h * 128, tw::make_smem_desc(a0_addr + 32 * c, 16, 512, 4), tw::make_smem_desc(bw_addr + 32 * c, 16, 512, 4),
-                              IDESC_128, t_sfa0 + 4 * c, t_sfbw + 4 * c, 1u);
+              tw::tc_mma_nvf4(acc + h * 128, op_desc(a0_addr + 32 * c), op_desc(bw_addr + 32 * c), IDESC_128,
+                              t_sfa0 + 4 * c, t_sfbw + 4 * c, 1u);
             if (p.cross && sel) {
 #pragma unroll
               for (int c = 0; c < 2; ++c)
-                tw::tc_mma_nvf4(acc + h * 128, tw::make_smem_desc(a1_addr + 32 * c, 16, 512, 4), tw::make_smem_desc(bw_addr + 32 * c, 16, 512, 4),
-                                IDESC_128, t_sfa1 + 4 * c, t_sfbw + 4 * c, 1u);
+                tw::tc_mma_nvf4(acc + h * 128, op_desc(a1_addr + 32 * c), op_desc(bw_addr + 32 * c), IDESC_128,
+                                t_sfa1 + 4 * c, t_sfbw + 4 * c, 1u);
             }
-            tw::tc_commit(emptyB + sbw);
+            tw::tc_commit(emptyW + sw);
           }
           tw::tc_commit(emptyA + sa0);
           if (sel) tw::tc_commit(emptyA + sa1);
         }
         if (ok) tw::tc_commit(accFull + stage);
+        tw::mbar_arrive(tabEmpty + it % C::TAB_SLOTS);
       }
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     }
-  } else {
+  } else if (warp >= C::FIRST_EPI_WARP) {
     // ------------------------------------------------------------------ epilogue
-    const int e = warp - 2;
-    const int quad = warp & 3;                     // TMEM lane quadrant this warp may read
-    const int group = e >> 2;                      // column group
-    uint8_t* stage_base = sOut + e * C::EPI_CHUNKS * C::STAGE_BYTES;
+    const int quad = warp & 3;                              // TMEM lane quadrant this warp may read
+    const int group = (warp - C::FIRST_EPI_WARP) >> 2;      // column group
     uint32_t it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
       const int mbi = tile / p.tiles_n, nt = tile % p.tiles_n;
-      const int n_rows = min(BN, p.n - nt * BN);
       const uint32_t stage = it % C::ACC_STAGES, aph = (it / C::ACC_STAGES) & 1;
       ok = tw::mbar_wait(accFull + stage, aph, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tw::tc_fence_after();
       const float alpha = __ldg(p.alpha);
-      // the previous tile's stores must have finished reading the staging buffers
-      if (lane == 0) tw::bulk_wait_read<0>();
-      __syncwarp();
       const uint32_t t_base = tmem + ((uint32_t)(quad * 32) << 16) + C::TM_ACC + stage * BN + group * C::EPI_COLS;
-#pragma unroll 1
-      for (int ch = 0; ch < C::EPI_CHUNKS; ++ch) {
-        uint8_t* buf = stage_base + ch * C::STAGE_BYTES;
+      uint32_t packed[C::EPI_COLS / 2];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t r[32];
-          tw::tmem_load_32x32(t_base + ch * 64 + half * 32, r);
-          tw::tmem_load_wait();
+      for (int part = 0; part < C::EPI_COLS / 32; ++part) {
+        uint32_t r[32];
+        tw::tmem_load_32x32(t_base + part * 32, r);
+        tw::tmem_load_wait();
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {            // four 16-byte pieces = 8 columns each
-            uint32_t w[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              float lo = __uint_as_float(r[j * 8 + 2 * q]) * alpha, hi = __uint_as_float(r[j * 8 + 2 * q + 1]) * alpha;
-              __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
-              w[q] = *reinterpret_cast<uint32_t*>(&b);
-            }
-            const int piece = half * 4 + j;         // 16-byte piece index within the 128-byte row
-            *reinterpret_cast<uint4*>(buf + lane * 128 + ((piece ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
+        for (int q = 0; q < 16; ++q) {
+          __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[2 * q]) * alpha, __uint_as_float(r[2 * q + 1]) * alpha);
+          packed[part * 16 + q] = *reinterpret_cast<uint32_t*>(&b);
         }
       }
-      // accumulator drained: hand the TMEM stage back before the global stores are issued
+      // accumulator drained into registers: hand the TMEM stage back before storing
       tw::tc_fence_before();
       __syncwarp();
       if (lane == 0) tw::mbar_arrive(accEmpty + stage);
-      tw::fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) {
-        for (int ch = 0; ch < C::EPI_CHUNKS; ++ch) {
-          const int col = nt * BN + group * C::EPI_COLS + ch * 64;
-          if (col < nt * BN + n_rows)
-            tw::tma_store_2d(&tm_out, stage_base + ch * C::STAGE_BYTES, col, mbi * 128 + quad * 32);
-        }
-        tw::bulk_commit();
+      const int row = mbi * 128 + quad * 32 + lane;
+      const int col = nt * BN + group * C::EPI_COLS;
+      if (row < p.m && col < p.n) {
+        uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)row * p.n + col);
+#pragma unroll
+        for (int j = 0; j < C::EPI_COLS / 8; ++j)
+          dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
       }
     }
-    if (lane == 0) tw::bulk_wait_all<0>();
   }
 
   tw::tc_fence_before();
@@ -380,7 +388,7 @@ template <int BN>
 int launch(int m, int n, int k, const void* a_codes, const void* w_codes, const void* sfa, const void* sfb, void* out,
            const float* alpha, void* workspace, cudaStream_t stream, const TwRepairIO* io, int sms) {
   using C = Cfg<BN>;
-  CUtensorMap tm_a, tm_w0, tm_w1, tm_out;
+  CUtensorMap tm_a, tm_w0, tm_w1;
   const int planes = io->na > 0 ? 2 : 1;
   {
     cuuint64_t dims[3] = {(cuuint64_t)k / 2, (cuuint64_t)io->mp, (cuuint64_t)planes};
@@ -405,13 +413,6 @@ int launch(int m, int n, int k, const void* a_codes, const void* w_codes, const 
                   CU_TENSOR_MAP_SWIZZLE_64B))
       return TW_ERR_TENSOR_MAP;
   }
-  {
-    cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)m};
-    cuuint64_t strides[1] = {(cuuint64_t)n * 2};
-    cuuint32_t box[2] = {64, 32};
-    if (!make_map(&tm_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
-      return TW_ERR_TENSOR_MAP;
-  }
   Params p{};
   p.sfa0 = static_cast<const uint8_t*>(sfa);
   p.sfa1 = io->a1s_swz;
@@ -419,6 +420,7 @@ int launch(int m, int n, int k, const void* a_codes, const void* w_codes, const 
   p.sfbw = io->wrs_swz;
   p.wi = io->wi; p.off = io->off; p.wloc = io->wloc; p.mask = io->mask;
   p.alpha = alpha;
+  p.out = static_cast<__nv_bfloat16*>(out);
   p.status = static_cast<int*>(workspace);
   p.m = m; p.mp = io->mp; p.n = n; p.k = k; p.na = io->na; p.hasw = io->hasw; p.cross = io->cross;
   p.shared = io->shared; p.dense = io->dense;
@@ -432,7 +434,7 @@ int launch(int m, int n, int k, const void* a_codes, const void* w_codes, const 
     configured = true;
   }
   const int grid = p.tiles < sms ? p.tiles : sms;
-  fused_kernel<BN><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tm_a, tm_w0, tm_w1, tm_out, p);
+  fused_kernel<BN><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tm_a, tm_w0, tm_w1, p);
   return cudaGetLastError() == cudaSuccess ? TW_OK : TW_ERR_LAUNCH;
 }
 
