@@ -69,6 +69,10 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+#ifdef TW_EXP_NOLOAD
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+  return;
+#endif
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -76,6 +80,12 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
+#ifdef TW_EXP_TESTWAIT
+  asm volatile(
+      "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+#endif
   asm volatile(
       "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
@@ -98,6 +108,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Same contract, for warps that wait long (epilogue, table builder): only lane 0 polls, with a
+// short sleep between polls, so that idle warps do not take issue slots from the single-thread
+// producer and MMA roles; the other lanes block at the warp barrier.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               long long limit_cycles = 4000000000LL) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) {
+    if (!mbar_try_wait(bar, parity)) {
+      long long start = clock64();
+      uint32_t polls = 0;
+      while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(64);
+        if ((++polls & 63u) == 0u) {
+          if (*abort_flag) { ok = 0; break; }
+          if (clock64() - start > limit_cycles) { *abort_flag = 1; ok = 0; break; }
+        }
+      }
+    }
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
+}
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(
@@ -112,17 +145,26 @@ __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const void* tmap, int x, int y, uint64_t* bar) {
+#ifdef TW_EXP_NOLOAD
+  return;
+#endif
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_u32(dst)), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void tma_load_3d(void* dst, const void* tmap, int x, int y, int z, uint64_t* bar) {
+#ifdef TW_EXP_NOLOAD
+  return;
+#endif
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
       ::"r"(smem_u32(dst)), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
 }
 // Untiled bulk copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+#ifdef TW_EXP_NOLOAD
+  return;
+#endif
   asm volatile(
       "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
       ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
@@ -154,18 +196,35 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t columns) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// Mainloop variant: the operands were written by the async proxy (TMA) and are read by the async
+// proxy (tcgen05), ordered by the mbarrier itself.
+__device__ __forceinline__ void tc_fence_after_load() {
+#ifndef TW_EXP_NOFENCE
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#endif
+}
 // Arrives once on `bar` when every tcgen05 operation issued so far by this thread has completed.
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
+#ifdef TW_EXP_ARRIVE
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+  return;
+#endif
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                ::"r"(smem_u32(bar)) : "memory");
 }
 // 32 rows x 16 bytes of shared memory -> 4 TMEM columns, replicated to the four lane quadrants.
 __device__ __forceinline__ void tc_copy_scales(uint32_t tmem_addr, uint64_t smem_desc) {
+#if defined(TW_EXP_NOMMA) || defined(TW_EXP_NOCP)
+  return;
+#endif
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(smem_desc) : "memory");
 }
 // D[tmem] (+)= A[smem] * B[smem]^T, E2M1 operands with one UE4M3 scale per 16 elements of K; K = 64.
 __device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+#if defined(TW_EXP_NOMMA) || defined(TW_EXP_CPONLY)
+  return;
+#endif
   asm volatile(
       "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
       "  tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p; }"
@@ -205,6 +264,11 @@ __device__ __forceinline__ void tmem_load_32x32(uint32_t taddr, uint32_t (&r)[32
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
+}
+// One 32-byte global store (32-byte aligned address).
+__device__ __forceinline__ void store_256(void* ptr, const uint32_t (&w)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
 }
 __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 

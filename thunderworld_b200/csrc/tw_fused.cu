@@ -6,57 +6,65 @@
 // tcgen05.mma kind::mxf4nvf4.block_scale into ONE fp32 accumulator in tensor memory; the epilogue
 // scales by the device scalar alpha and rounds to bf16 once. Term structure follows the reference
 // (thunderworld_fp4/_native.py:11-62; cutlass/repair_collective.cuh:117-132); what differs is the
-// schedule: terms are interleaved per K128 block so that each operand tile is fetched once per
-// output tile: per kb the CTA loads A0[kb], W0[kb], A1[kb] if selected and the W1 tiles of (nb,kb),
-// and issues A0W0, A1W0, A0W1, A1W1 back to back.
+// schedule. The K loop advances in steps of 256 (two blocks of the K128 repair lattice): a "base
+// stage" holds A0 (128 x 128 B) and W0 (BN x 128 B) of the step with their scales and costs the
+// single-thread producer and MMA roles one barrier round trip; the repair operands of the same
+// step (A1 blocks, W1 tiles: "units" of 128 x 64 B) arrive through a second ring and are multiplied
+// against the resident base stage, so W0 is fetched once for A0 and A1, and A0 once for W0 and W1.
 //
 // CTA = one 128 x BN output tile at a time (persistent over tiles), warp-specialised:
-//   warp 0      producer: TMA loads of code tiles (64-byte swizzle) + bulk copies of scale atoms
+//   warp 0      producer of base stages (TMA, 128-byte swizzle; bulk copies of scale atoms)
 //   warp 1      MMA issuer: scale atoms smem -> TMEM (tcgen05.cp), MMAs, commits
-//   warp 2      builds the per-tile term tables (A-support bytes, W1 bank positions) ahead of use
+//   warp 2      producer of repair units (TMA, 64-byte swizzle)
+//   warp 3      builds the per-tile term tables (A-support bits, W1 bank positions) ahead of use
 //   warps 4-11  epilogue: TMEM -> registers -> bf16 -> global (16-byte stores), TMEM released first
-// Operand rings: A slots (128 rows x 64 B codes + 1 KB scales), W0 slots (BN rows x 64 B codes +
-// BN/128 KB scales) and W1 slots (128 rows). No cluster, no multicast.
+// No cluster, no multicast.
 #include <cuda.h>
 #include "tw_common.cuh"
 #include "../../include/twb200.h"
 
 namespace {
 
-constexpr int KB_MAX = 256;               // K <= 32768
-constexpr int A_TILE = 128 * 64;          // bytes of one 128 x K128 code tile
+constexpr int KB_MAX = 128;               // K <= 16384
+constexpr int UNIT_TILE = 128 * 64;       // bytes of one 128-row x K128 code tile
 constexpr int SF_ATOM = 1024;             // bytes of the scales of 128 rows x K128
 
 template <int BN> struct Cfg {
   static constexpr int HALVES = BN / 128;
-  static constexpr int A_SLOTS = 7;                           // A0 / A1 tiles
-  static constexpr int B_SLOTS = BN == 256 ? 6 : 8;           // W0 tiles (BN rows)
-  static constexpr int W_SLOTS = 4;                           // W1 tiles (128 rows)
+  static constexpr int STAGES = BN == 256 ? 3 : 4;            // base stages (K256 of A0 and W0)
+  static constexpr int A1_SLOTS = 3;                          // A1 units
+  static constexpr int W1_SLOTS = 3;                          // W1 units
   static constexpr int TAB_SLOTS = 3;                         // per-tile term tables built ahead
   static constexpr int ACC_STAGES = BN == 256 ? 1 : 2;
   static constexpr int EPI_WARPS = 8;
-  static constexpr int FIRST_EPI_WARP = 4;                    // warps 0..3: producer, MMA, tables, spare
+  static constexpr int FIRST_EPI_WARP = 4;
   static constexpr int EPI_GROUPS = EPI_WARPS / 4;            // column groups per lane quadrant
   static constexpr int EPI_COLS = BN / EPI_GROUPS;            // columns per epilogue warp
   static constexpr int THREADS = (FIRST_EPI_WARP + EPI_WARPS) * 32;
-  static constexpr int B_TILE = BN * 64;
+  static constexpr int A0_TILE = 128 * 128;                   // 128 rows x K256
+  static constexpr int W0_TILE = BN * 128;
+  static constexpr int STAGE_SF = (1 + HALVES) * 2 * SF_ATOM; // A0 scales then W0 scales per half
   // shared-memory carve-up (offsets from a 1024-aligned base)
-  static constexpr int OFF_A = 0;
-  static constexpr int OFF_B = OFF_A + A_SLOTS * A_TILE;
-  static constexpr int OFF_W = OFF_B + B_SLOTS * B_TILE;
-  static constexpr int OFF_SFA = OFF_W + W_SLOTS * A_TILE;
-  static constexpr int OFF_SFB = OFF_SFA + A_SLOTS * SF_ATOM;
-  static constexpr int OFF_SFW = OFF_SFB + B_SLOTS * HALVES * SF_ATOM;
-  static constexpr int OFF_TAB = OFF_SFW + W_SLOTS * SF_ATOM;
-  static constexpr int TAB_BYTES = HALVES * KB_MAX * 4 + KB_MAX;
+  static constexpr int OFF_A0 = 0;
+  static constexpr int OFF_W0 = OFF_A0 + STAGES * A0_TILE;
+  static constexpr int OFF_A1 = OFF_W0 + STAGES * W0_TILE;
+  static constexpr int OFF_W1 = OFF_A1 + A1_SLOTS * UNIT_TILE;
+  static constexpr int OFF_SF0 = OFF_W1 + W1_SLOTS * UNIT_TILE;
+  static constexpr int OFF_SFA1 = OFF_SF0 + STAGES * STAGE_SF;
+  static constexpr int OFF_SFW1 = OFF_SFA1 + A1_SLOTS * SF_ATOM;
+  static constexpr int OFF_TAB = OFF_SFW1 + W1_SLOTS * SF_ATOM;
+  static constexpr int TAB_BYTES = HALVES * KB_MAX * 4 + (HALVES + 1) * (KB_MAX / 32) * 4;
   static constexpr int OFF_BAR = OFF_TAB + TAB_SLOTS * TAB_BYTES;
-  static constexpr int NUM_BARS = 2 * A_SLOTS + 2 * B_SLOTS + 2 * W_SLOTS + 2 * TAB_SLOTS + 2 * ACC_STAGES;
+  static constexpr int NUM_BARS = 2 * STAGES + 2 * A1_SLOTS + 2 * W1_SLOTS + 2 * TAB_SLOTS + 2 * ACC_STAGES;
   static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 64 + 1024;  // + alignment slack
-  // tensor-memory columns
+  // tensor-memory columns: accumulators, then double-buffered scale regions
   static constexpr int TM_ACC = 0;
-  static constexpr int TM_SF = ACC_STAGES * BN;                          // 256
-  static constexpr int TM_SFA0 = TM_SF, TM_SFA1 = TM_SF + 16, TM_SFB0 = TM_SF + 32, TM_SFBW = TM_SF + 32 + 2 * 4 * HALVES * 2;
+  static constexpr int TM_SFA0 = ACC_STAGES * BN;                        // 2 x 16 columns
+  static constexpr int TM_SFB0 = TM_SFA0 + 32;                           // 2 x 16*HALVES columns
+  static constexpr int TM_SFA1 = TM_SFB0 + 32 * HALVES;                  // 2 x 2 x 8 columns (two units per step)
+  static constexpr int TM_SFW1 = TM_SFA1 + 32;                           // 2 x 8 columns
   static constexpr int TM_COLS = 512;
+  static_assert(TM_SFW1 + 16 <= TM_COLS, "tensor memory budget");
 };
 static_assert(Cfg<256>::SMEM_BYTES <= 232448 && Cfg<128>::SMEM_BYTES <= 232448, "shared memory budget");
 
@@ -74,11 +82,13 @@ struct Params {
   int kb, nb, mb, tiles_n, tiles;
 };
 
-// Per-tile term table: for every kb whether A1 is selected and, for each N128 half of the tile,
-// the bank position of the W1 tile at (nb, kb) or -1.
+// Per-tile term table, built ahead of use by its own warp: one bit per kb for "A1 selected" and
+// for "a W1 tile exists at (nb, kb)" per N128 half of the tile (the MMA issuer and the producers
+// walk these bits in registers), and the bank position of each W1 tile for the unit producer.
 template <int BN> struct TermTable {
-  int w1[Cfg<BN>::HALVES][KB_MAX];
-  uint8_t a1[KB_MAX];
+  int w1loc[Cfg<BN>::HALVES][KB_MAX];
+  uint32_t w1bits[Cfg<BN>::HALVES][KB_MAX / 32];
+  uint32_t a1bits[KB_MAX / 32];
 };
 
 template <int BN>
@@ -92,42 +102,47 @@ __device__ __forceinline__ void build_table(TermTable<BN>& tab, const Params& p,
     begin[h] = use ? p.off[nb] : 0;
     end[h] = use ? p.off[nb + 1] : 0;
   }
-  for (int kb = lane; kb < p.kb; kb += 32) {
-    tab.a1[kb] = p.na == p.kb ? 1 : (p.na > 0 ? p.mask[mbi * p.kb + kb] : 0);
+  const int words = (p.kb + 31) / 32;
+  for (int w = 0; w < words; ++w) {
+    const int kb = w * 32 + lane;
+    const bool in = kb < p.kb;
+    const bool sel = in && (p.na == p.kb || (p.na > 0 && p.mask[mbi * p.kb + kb] != 0));
+    const uint32_t abits = __ballot_sync(0xffffffffu, sel);
+    if (lane == 0) tab.a1bits[w] = abits;
 #pragma unroll
     for (int h = 0; h < H; ++h) {
-      const int nb = nt * H + h;
-      tab.w1[h][kb] = (p.hasw && p.dense && nb < p.nb) ? nb * p.kb + kb : -1;
+      const bool dense = in && p.hasw && p.dense && (nt * H + h) < p.nb;
+      if (in) tab.w1loc[h][kb] = dense ? (nt * H + h) * p.kb + kb : -1;
+      const uint32_t wb = __ballot_sync(0xffffffffu, dense);
+      if (lane == 0) tab.w1bits[h][w] = wb;
     }
   }
   __syncwarp();
 #pragma unroll
   for (int h = 0; h < H; ++h)
-    for (int s = begin[h] + lane; s < end[h]; s += 32) tab.w1[h][p.wi[s]] = p.shared ? p.wloc[s] : s;
+    for (int s = begin[h] + lane; s < end[h]; s += 32) {
+      const int kb = p.wi[s];
+      tab.w1loc[h][kb] = p.shared ? p.wloc[s] : s;
+      atomicOr(&tab.w1bits[h][kb >> 5], 1u << (kb & 31));
+    }
   __syncwarp();
 }
 
 template <int BN>
 __global__ void __launch_bounds__(Cfg<BN>::THREADS, 1)
-fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w0,
-             const __grid_constant__ CUtensorMap tm_w1, const Params p) {
+fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
+             const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1, const Params p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sA = smem + C::OFF_A;
-  uint8_t* sB = smem + C::OFF_B;
-  uint8_t* sW = smem + C::OFF_W;
-  uint8_t* sSFA = smem + C::OFF_SFA;
-  uint8_t* sSFB = smem + C::OFF_SFB;
-  uint8_t* sSFW = smem + C::OFF_SFW;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
-  uint64_t* fullA = bars;
-  uint64_t* emptyA = fullA + C::A_SLOTS;
-  uint64_t* fullB = emptyA + C::A_SLOTS;
-  uint64_t* emptyB = fullB + C::B_SLOTS;
-  uint64_t* fullW = emptyB + C::B_SLOTS;
-  uint64_t* emptyW = fullW + C::W_SLOTS;
-  uint64_t* tabFull = emptyW + C::W_SLOTS;
+  uint64_t* fullS = bars;                       // base stages
+  uint64_t* emptyS = fullS + C::STAGES;
+  uint64_t* fullA1 = emptyS + C::STAGES;        // A1 units
+  uint64_t* emptyA1 = fullA1 + C::A1_SLOTS;
+  uint64_t* fullW1 = emptyA1 + C::A1_SLOTS;     // W1 units
+  uint64_t* emptyW1 = fullW1 + C::W1_SLOTS;
+  uint64_t* tabFull = emptyW1 + C::W1_SLOTS;
   uint64_t* tabEmpty = tabFull + C::TAB_SLOTS;
   uint64_t* accFull = tabEmpty + C::TAB_SLOTS;
   uint64_t* accEmpty = accFull + C::ACC_STAGES;
@@ -138,16 +153,18 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int steps = (p.kb + 1) / 2;             // K256 steps; the last one may hold a single K128 block
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < C::A_SLOTS; ++i) { tw::mbar_init(fullA + i, 1); tw::mbar_init(emptyA + i, 1); }
-    for (int i = 0; i < C::B_SLOTS; ++i) { tw::mbar_init(fullB + i, 1); tw::mbar_init(emptyB + i, 1); }
-    for (int i = 0; i < C::W_SLOTS; ++i) { tw::mbar_init(fullW + i, 1); tw::mbar_init(emptyW + i, 1); }
+    for (int i = 0; i < C::STAGES; ++i) { tw::mbar_init(fullS + i, 1); tw::mbar_init(emptyS + i, 1); }
+    for (int i = 0; i < C::A1_SLOTS; ++i) { tw::mbar_init(fullA1 + i, 1); tw::mbar_init(emptyA1 + i, 1); }
+    for (int i = 0; i < C::W1_SLOTS; ++i) { tw::mbar_init(fullW1 + i, 1); tw::mbar_init(emptyW1 + i, 1); }
     for (int i = 0; i < C::TAB_SLOTS; ++i) { tw::mbar_init(tabFull + i, 1); tw::mbar_init(tabEmpty + i, 2); }
     for (int i = 0; i < C::ACC_STAGES; ++i) { tw::mbar_init(accFull + i, 1); tw::mbar_init(accEmpty + i, C::EPI_WARPS); }
     *abort_flag = 0;
     tw::fence_barrier_init();
-    tw::tma_prefetch_desc(&tm_a); tw::tma_prefetch_desc(&tm_w0); tw::tma_prefetch_desc(&tm_w1);
+    tw::tma_prefetch_desc(&tm_a0); tw::tma_prefetch_desc(&tm_a1);
+    tw::tma_prefetch_desc(&tm_w0); tw::tma_prefetch_desc(&tm_w1);
   }
   if (warp == 1) { tw::tmem_alloc(tmem_slot, C::TM_COLS); tw::tmem_relinquish(); }
   tw::tc_fence_before();
@@ -155,198 +172,267 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   tw::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 2) {
+  if (warp == 3) {
     // ------------------------------------------------------------------ term tables, built ahead
     uint32_t it = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
-      ok = tw::mbar_wait(tabEmpty + it % C::TAB_SLOTS, ((it / C::TAB_SLOTS) & 1) ^ 1, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+    for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++it) {
+      if (!tw::mbar_wait_warp(tabEmpty + it % C::TAB_SLOTS, ((it / C::TAB_SLOTS) & 1) ^ 1, abort_flag)) break;
       build_table<BN>(table(it), p, tile / p.tiles_n, tile % p.tiles_n, lane);
       if (lane == 0) tw::mbar_arrive(tabFull + it % C::TAB_SLOTS);
     }
   } else if (warp == 0) {
-    // ------------------------------------------------------------------ producer (one thread)
+    // ------------------------------------------------------------------ producer of base stages
+    // Needs no term table: one stage per K256 step of every tile.
     if (lane == 0) {
-      uint32_t ia = 0, ib = 0, iw = 0, it = 0;
+      uint32_t is = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x) {
+        const int mbi = tile / p.tiles_n, nt = tile % p.tiles_n;
+        const int n_rows = min(BN, p.n - nt * BN);            // 128 or BN
+        for (int st = 0; st < steps && ok; ++st, ++is) {
+          const uint32_t s = is % C::STAGES, ph = (is / C::STAGES) & 1;
+          const int kb0 = 2 * st, nk = min(2, p.kb - kb0);     // K128 blocks in this step
+          ok = tw::mbar_wait(emptyS + s, ph ^ 1, abort_flag);
+          if (!ok) break;
+          // TMA always delivers the full box (out-of-range K reads as zero codes)
+          tw::mbar_expect_tx(fullS + s, C::A0_TILE + (uint32_t)n_rows * 128 + (uint32_t)(1 + n_rows / 128) * nk * SF_ATOM);
+          tw::tma_load_3d(smem + C::OFF_A0 + s * C::A0_TILE, &tm_a0, kb0 * 64, mbi * 128, 0, fullS + s);
+          tw::tma_load_2d(smem + C::OFF_W0 + s * C::W0_TILE, &tm_w0, kb0 * 64, nt * BN, fullS + s);
+          uint8_t* sf = smem + C::OFF_SF0 + s * C::STAGE_SF;
+          tw::bulk_load(sf, p.sfa0 + ((size_t)mbi * p.kb + kb0) * SF_ATOM, nk * SF_ATOM, fullS + s);
+          for (int h = 0; h < n_rows / 128; ++h)
+            tw::bulk_load(sf + (1 + h) * 2 * SF_ATOM, p.sfb0 + ((size_t)(nt * C::HALVES + h) * p.kb + kb0) * SF_ATOM,
+                          nk * SF_ATOM, fullS + s);
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ producer of repair units
+    // Per step, in the order the MMA issuer consumes them: A1(kb0), A1(kb1), then W1 tiles by (kb, half).
+    if (lane == 0) {
+      uint32_t ia = 0, iw = 0, it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
-        const int mbi = tile / p.tiles_n, nt = tile % p.tiles_n;
+        const int mbi = tile / p.tiles_n;
         const TermTable<BN>& tab = table(it);
         ok = tw::mbar_wait(tabFull + it % C::TAB_SLOTS, (it / C::TAB_SLOTS) & 1, abort_flag);
-        const int n_rows = min(BN, p.n - nt * BN);            // 128 or BN
-        for (int kb = 0; kb < p.kb && ok; ++kb) {
-          const bool sel = tab.a1[kb] != 0;
-          auto load_a = [&](int plane) {
-            const uint32_t s = ia % C::A_SLOTS, ph = (ia / C::A_SLOTS) & 1; ++ia;
-            if (!tw::mbar_wait(emptyA + s, ph ^ 1, abort_flag)) return false;
-            tw::mbar_expect_tx(fullA + s, A_TILE + SF_ATOM);
-            tw::tma_load_3d(sA + s * A_TILE, &tm_a, kb * 64, mbi * 128, plane, fullA + s);
-            const uint8_t* sf = (plane ? p.sfa1 : p.sfa0) + ((size_t)mbi * p.kb + kb) * SF_ATOM;
-            tw::bulk_load(sSFA + s * SF_ATOM, sf, SF_ATOM, fullA + s);
-            return true;
-          };
-          ok = load_a(0);
-          if (!ok) break;
-          {
-            const uint32_t s = ib % C::B_SLOTS, ph = (ib / C::B_SLOTS) & 1; ++ib;
-            ok = tw::mbar_wait(emptyB + s, ph ^ 1, abort_flag);
-            if (!ok) break;
-            tw::mbar_expect_tx(fullB + s, (uint32_t)n_rows * 64 + (uint32_t)(n_rows / 128) * SF_ATOM);
-            tw::tma_load_2d(sB + s * C::B_TILE, &tm_w0, kb * 64, nt * BN, fullB + s);
-            for (int h = 0; h < n_rows / 128; ++h) {
-              const uint8_t* sf = p.sfb0 + ((size_t)(nt * C::HALVES + h) * p.kb + kb) * SF_ATOM;
-              tw::bulk_load(sSFB + (s * C::HALVES + h) * SF_ATOM, sf, SF_ATOM, fullB + s);
+        uint32_t abits = 0, wbits[C::HALVES] = {};
+        for (int st = 0; st < steps && ok; ++st) {
+          const int kb0 = 2 * st;
+          if ((kb0 & 31) == 0) {
+            abits = tab.a1bits[kb0 >> 5];
+#pragma unroll
+            for (int h = 0; h < C::HALVES; ++h) wbits[h] = tab.w1bits[h][kb0 >> 5];
+          }
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            if (!((abits >> j) & 1u) || !ok) continue;
+            const uint32_t s = ia % C::A1_SLOTS, ph = (ia / C::A1_SLOTS) & 1; ++ia;
+            ok = tw::mbar_wait(emptyA1 + s, ph ^ 1, abort_flag);
+            if (!ok) continue;
+            tw::mbar_expect_tx(fullA1 + s, UNIT_TILE + SF_ATOM);
+            tw::tma_load_3d(smem + C::OFF_A1 + s * UNIT_TILE, &tm_a1, (kb0 + j) * 64, mbi * 128, 1, fullA1 + s);
+            tw::bulk_load(smem + C::OFF_SFA1 + s * SF_ATOM, p.sfa1 + ((size_t)mbi * p.kb + kb0 + j) * SF_ATOM, SF_ATOM, fullA1 + s);
+          }
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int h = 0; h < C::HALVES; ++h) {
+              if (!((wbits[h] >> j) & 1u) || !ok) continue;
+              const int loc = tab.w1loc[h][kb0 + j];
+              const uint32_t s = iw % C::W1_SLOTS, ph = (iw / C::W1_SLOTS) & 1; ++iw;
+              ok = tw::mbar_wait(emptyW1 + s, ph ^ 1, abort_flag);
+              if (!ok) continue;
+              tw::mbar_expect_tx(fullW1 + s, UNIT_TILE + SF_ATOM);
+              tw::tma_load_2d(smem + C::OFF_W1 + s * UNIT_TILE, &tm_w1, 0, loc * 128, fullW1 + s);
+              tw::bulk_load(smem + C::OFF_SFW1 + s * SF_ATOM, p.sfbw + (size_t)loc * SF_ATOM, SF_ATOM, fullW1 + s);
             }
           }
-          if (sel) { ok = load_a(1); if (!ok) break; }
-          for (int h = 0; h < C::HALVES && ok; ++h) {
-            const int loc = tab.w1[h][kb];
-            if (loc < 0) continue;
-            const uint32_t s = iw % C::W_SLOTS, ph = (iw / C::W_SLOTS) & 1; ++iw;
-            ok = tw::mbar_wait(emptyW + s, ph ^ 1, abort_flag);
-            if (!ok) break;
-            tw::mbar_expect_tx(fullW + s, A_TILE + SF_ATOM);
-            tw::tma_load_2d(sW + s * A_TILE, &tm_w1, 0, loc * 128, fullW + s);
-            tw::bulk_load(sSFW + s * SF_ATOM, p.sfbw + (size_t)loc * SF_ATOM, SF_ATOM, fullW + s);
-          }
+          abits >>= 2;
+#pragma unroll
+          for (int h = 0; h < C::HALVES; ++h) wbits[h] >>= 2;
         }
         tw::mbar_arrive(tabEmpty + it % C::TAB_SLOTS);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (one thread)
+    // One thread issues every tcgen05 operation, so its instruction stream is kept short: slot
+    // counters advance incrementally, descriptors are a constant high word plus (address >> 4).
     if (lane == 0) {
-      uint32_t ia = 0, ib = 0, iw = 0, it = 0;
       bool ok = true;
       constexpr uint32_t IDESC_FULL = tw::make_idesc_nvf4(128, BN);
       constexpr uint32_t IDESC_128 = tw::make_idesc_nvf4(128, 128);
-      const uint64_t desc_hi = tw::make_smem_desc(0, 16, 512, 4);   // 64-byte swizzle, 8-row groups 512 B apart
-      const uint64_t sf_hi = tw::make_smem_desc(0, 0, 128, 0);      // scale atom: 32 rows x 16 B, no swizzle
-      auto op_desc = [&](uint32_t addr) { return desc_hi | (uint64_t)((addr >> 4) & 0x3fffu); };
-      auto sf_desc = [&](uint32_t addr) { return sf_hi | (uint64_t)((addr >> 4) & 0x3fffu); };
+      constexpr uint64_t D128 = (uint64_t(1) << 46) | (uint64_t(2) << 61) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 16);
+      constexpr uint64_t D64 = (uint64_t(1) << 46) | (uint64_t(4) << 61) | (uint64_t(512 >> 4) << 32) | (uint64_t(1) << 16);
+      constexpr uint64_t DSF = (uint64_t(1) << 46) | (uint64_t(128 >> 4) << 32);
+      const uint32_t smem_u = tw::smem_u32(smem);
+      const uint32_t a0_base = (smem_u + C::OFF_A0) >> 4, w0_base = (smem_u + C::OFF_W0) >> 4;
+      const uint32_t sf0_base = (smem_u + C::OFF_SF0) >> 4;
+      const uint32_t a1_base = (smem_u + C::OFF_A1) >> 4, w1_base = (smem_u + C::OFF_W1) >> 4;
+      const uint32_t sfa1_base = (smem_u + C::OFF_SFA1) >> 4, sfw1_base = (smem_u + C::OFF_SFW1) >> 4;
+      const uint32_t t_sfa0_b = tmem + C::TM_SFA0, t_sfb0_b = tmem + C::TM_SFB0;
+      uint32_t s = 0, ph = 0;                  // base stage slot / phase
+      uint32_t sa = 0, pa = 0, sw = 0, pw = 0; // unit slots / phases
+      uint32_t it = 0, tsl = 0, tph = 0;       // tile counter, table slot / phase
       for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
         const int nt = tile % p.tiles_n;
-        const TermTable<BN>& tab = table(it);
-        ok = tw::mbar_wait(tabFull + it % C::TAB_SLOTS, (it / C::TAB_SLOTS) & 1, abort_flag);
+        const TermTable<BN>& tab = *reinterpret_cast<const TermTable<BN>*>(smem + C::OFF_TAB + tsl * C::TAB_BYTES);
         const int n_rows = min(BN, p.n - nt * BN);
         const uint32_t idesc_base = n_rows == BN ? IDESC_FULL : IDESC_128;
         const uint32_t stage = it % C::ACC_STAGES, aph = (it / C::ACC_STAGES) & 1;
-        ok = ok && tw::mbar_wait(accEmpty + stage, aph ^ 1, abort_flag);
+        ok = tw::mbar_wait(tabFull + tsl, tph, abort_flag) && tw::mbar_wait(accEmpty + stage, aph ^ 1, abort_flag);
         tw::tc_fence_after();
         const uint32_t acc = tmem + C::TM_ACC + stage * BN;
-        for (int kb = 0; kb < p.kb && ok; ++kb) {
-          const bool sel = tab.a1[kb] != 0;
-          const uint32_t par = kb & 1;                           // double-buffered TMEM scale regions
-          const uint32_t t_sfa0 = tmem + C::TM_SFA0 + par * 8, t_sfa1 = tmem + C::TM_SFA1 + par * 8;
-          const uint32_t t_sfb0 = tmem + C::TM_SFB0 + par * 8 * C::HALVES;
-          // A0 and W0
-          const uint32_t sa0 = ia % C::A_SLOTS, pa0 = (ia / C::A_SLOTS) & 1; ++ia;
-          const uint32_t sb0 = ib % C::B_SLOTS, pb0 = (ib / C::B_SLOTS) & 1; ++ib;
-          ok = tw::mbar_wait(fullA + sa0, pa0, abort_flag) && tw::mbar_wait(fullB + sb0, pb0, abort_flag);
+        uint32_t abits = 0, wbits[C::HALVES] = {};
+        for (int st = 0; st < steps && ok; ++st) {
+          const int kb0 = 2 * st;
+          const int nq = p.kb - kb0 >= 2 ? 4 : 2;                  // K64 slices in this step
+          if ((kb0 & 31) == 0) {
+            abits = tab.a1bits[kb0 >> 5];
+#pragma unroll
+            for (int h = 0; h < C::HALVES; ++h) wbits[h] = tab.w1bits[h][kb0 >> 5];
+          }
+          ok = tw::mbar_wait(fullS + s, ph, abort_flag);
           if (!ok) break;
-          tw::tc_fence_after();
-          const uint32_t a0_addr = tw::smem_u32(sA + sa0 * A_TILE), b0_addr = tw::smem_u32(sB + sb0 * C::B_TILE);
-          const uint32_t sfa0_addr = tw::smem_u32(sSFA + sa0 * SF_ATOM), sfb0_addr = tw::smem_u32(sSFB + sb0 * C::HALVES * SF_ATOM);
+          tw::tc_fence_after_load();
+          const uint32_t a0_lo = a0_base + s * (C::A0_TILE >> 4), w0_lo = w0_base + s * (C::W0_TILE >> 4);
+          const uint32_t sf_lo = sf0_base + s * (C::STAGE_SF >> 4);
+#ifdef TW_EXP_DB
+          const uint32_t t_sfa0 = t_sfa0_b + (st & 1) * 16, t_sfb0 = t_sfb0_b + (st & 1) * 16 * C::HALVES;
+#else
+          const uint32_t t_sfa0 = t_sfa0_b, t_sfb0 = t_sfb0_b;
+#endif
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            tw::tc_copy_scales(t_sfa0 + 4 * c, sf_desc(sfa0_addr + c * 512));
+          for (int q = 0; q < 4; ++q) {                            // scales of the q-th K64 slice into TMEM
+            if (q < nq) {
+              tw::tc_copy_scales(t_sfa0 + 4 * q, DSF | (sf_lo + q * 32));
+#ifndef TW_EXP_SFA_ONLY
 #pragma unroll
-            for (int h = 0; h < C::HALVES; ++h)
-              if (h * 128 < n_rows)
-                tw::tc_copy_scales(t_sfb0 + 4 * C::HALVES * c + 4 * h, sf_desc(sfb0_addr + h * SF_ATOM + c * 512));
+              for (int h = 0; h < C::HALVES; ++h)
+                if (h * 128 < n_rows)
+                  tw::tc_copy_scales(t_sfb0 + 4 * C::HALVES * q + 4 * h, DSF | (sf_lo + (1 + h) * 128 + q * 32));
+#endif
+            }
           }
 #pragma unroll
-          for (int c = 0; c < 2; ++c)
-            tw::tc_mma_nvf4(acc, op_desc(a0_addr + 32 * c), op_desc(b0_addr + 32 * c), idesc_base, t_sfa0 + 4 * c,
-                            t_sfb0 + 4 * C::HALVES * c, (kb | c) != 0);
-          // A1 against the same W0 tile
-          uint32_t sa1 = 0, a1_addr = 0;
-          if (sel) {
-            sa1 = ia % C::A_SLOTS; const uint32_t pa1 = (ia / C::A_SLOTS) & 1; ++ia;
-            ok = tw::mbar_wait(fullA + sa1, pa1, abort_flag);
-            if (!ok) break;
-            tw::tc_fence_after();
-            a1_addr = tw::smem_u32(sA + sa1 * A_TILE);
-            const uint32_t sfa1_addr = tw::smem_u32(sSFA + sa1 * SF_ATOM);
+          for (int q = 0; q < 4; ++q)                              // A0 W0
+            if (q < nq)
+              tw::tc_mma_nvf4(acc, D128 | (a0_lo + 2 * q), D128 | (w0_lo + 2 * q), idesc_base, t_sfa0 + 4 * q,
+                              t_sfb0 + 4 * C::HALVES * q, (st | q) != 0);
+          const uint32_t ab = abits & 3u;
+          uint32_t wb = 0;
 #pragma unroll
-            for (int c = 0; c < 2; ++c) tw::tc_copy_scales(t_sfa1 + 4 * c, sf_desc(sfa1_addr + c * 512));
+          for (int h = 0; h < C::HALVES; ++h) wb |= (wbits[h] & 3u) << (2 * h);
+          if (ab | wb) {
+            // A1 blocks of this step against the resident W0 stage
+            uint32_t a1_lo[2] = {0, 0}, a1_bar[2] = {0, 0};
 #pragma unroll
-            for (int c = 0; c < 2; ++c)
-              tw::tc_mma_nvf4(acc, op_desc(a1_addr + 32 * c), op_desc(b0_addr + 32 * c), idesc_base, t_sfa1 + 4 * c,
-                              t_sfb0 + 4 * C::HALVES * c, 1u);
-          }
-          tw::tc_commit(emptyB + sb0);
-          // W1 tiles of this kb: 128-column MMAs into the matching half of the accumulator
-          for (int h = 0; h < C::HALVES && ok; ++h) {
-            if (tab.w1[h][kb] < 0) continue;
-            const uint32_t sw = iw % C::W_SLOTS, pw = (iw / C::W_SLOTS) & 1;
-            const uint32_t t_sfbw = tmem + C::TM_SFBW + ((iw & 1) * 8);
-            ++iw;
-            ok = tw::mbar_wait(fullW + sw, pw, abort_flag);
-            if (!ok) break;
-            tw::tc_fence_after();
-            const uint32_t bw_addr = tw::smem_u32(sW + sw * A_TILE), sfw_addr = tw::smem_u32(sSFW + sw * SF_ATOM);
+            for (int j = 0; j < 2; ++j) {
+              if (!((ab >> j) & 1u) || !ok) continue;
+              ok = tw::mbar_wait(fullA1 + sa, pa, abort_flag);
+              if (!ok) continue;
+              tw::tc_fence_after_load();
+              a1_lo[j] = a1_base + sa * (UNIT_TILE >> 4);
+              a1_bar[j] = sa;
+              const uint32_t sfa1_lo = sfa1_base + sa * (SF_ATOM >> 4);
+              const uint32_t t_sfa1 = tmem + C::TM_SFA1 + j * 8;
 #pragma unroll
-            for (int c = 0; c < 2; ++c) tw::tc_copy_scales(t_sfbw + 4 * c, sf_desc(sfw_addr + c * 512));
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
-              tw::tc_mma_nvf4(acc + h * 128, op_desc(a0_addr + 32 * c), op_desc(bw_addr + 32 * c), IDESC_128,
-                              t_sfa0 + 4 * c, t_sfbw + 4 * c, 1u);
-            if (p.cross && sel) {
+              for (int c = 0; c < 2; ++c) tw::tc_copy_scales(t_sfa1 + 4 * c, DSF | (sfa1_lo + c * 32));
 #pragma unroll
               for (int c = 0; c < 2; ++c)
-                tw::tc_mma_nvf4(acc + h * 128, op_desc(a1_addr + 32 * c), op_desc(bw_addr + 32 * c), IDESC_128,
-                                t_sfa1 + 4 * c, t_sfbw + 4 * c, 1u);
+                tw::tc_mma_nvf4(acc, D64 | (a1_lo[j] + 2 * c), D128 | (w0_lo + 4 * j + 2 * c), idesc_base,
+                                t_sfa1 + 4 * c, t_sfb0 + 4 * C::HALVES * (2 * j + c), 1u);
+              if (!p.cross) tw::tc_commit(emptyA1 + sa);
+              if (++sa == C::A1_SLOTS) { sa = 0; pa ^= 1; }
             }
-            tw::tc_commit(emptyW + sw);
+            // W1 tiles of this step: 128-column MMAs into the matching half of the accumulator
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+#pragma unroll
+              for (int h = 0; h < C::HALVES; ++h) {
+                if (!((wb >> (2 * h + j)) & 1u) || !ok) continue;
+                ok = tw::mbar_wait(fullW1 + sw, pw, abort_flag);
+                if (!ok) continue;
+                tw::tc_fence_after_load();
+                const uint32_t w1_lo = w1_base + sw * (UNIT_TILE >> 4), sfw1_lo = sfw1_base + sw * (SF_ATOM >> 4);
+                const uint32_t t_sfw1 = tmem + C::TM_SFW1;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) tw::tc_copy_scales(t_sfw1 + 4 * c, DSF | (sfw1_lo + c * 32));
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+                  tw::tc_mma_nvf4(acc + h * 128, D128 | (a0_lo + 4 * j + 2 * c), D64 | (w1_lo + 2 * c), IDESC_128,
+                                  t_sfa0 + 4 * (2 * j + c), t_sfw1 + 4 * c, 1u);
+                if (p.cross && ((ab >> j) & 1u)) {
+                  const uint32_t t_sfa1 = tmem + C::TM_SFA1 + j * 8;
+#pragma unroll
+                  for (int c = 0; c < 2; ++c)
+                    tw::tc_mma_nvf4(acc + h * 128, D64 | (a1_lo[j] + 2 * c), D64 | (w1_lo + 2 * c), IDESC_128,
+                                    t_sfa1 + 4 * c, t_sfw1 + 4 * c, 1u);
+                }
+                tw::tc_commit(emptyW1 + sw);
+                if (++sw == C::W1_SLOTS) { sw = 0; pw ^= 1; }
+              }
+            }
+            if (p.cross) {
+#pragma unroll
+              for (int j = 0; j < 2; ++j)
+                if ((ab >> j) & 1u) tw::tc_commit(emptyA1 + a1_bar[j]);
+            }
           }
-          tw::tc_commit(emptyA + sa0);
-          if (sel) tw::tc_commit(emptyA + sa1);
+          tw::tc_commit(emptyS + s);
+          if (++s == C::STAGES) { s = 0; ph ^= 1; }
+          abits >>= 2;
+#pragma unroll
+          for (int h = 0; h < C::HALVES; ++h) wbits[h] >>= 2;
         }
         if (ok) tw::tc_commit(accFull + stage);
-        tw::mbar_arrive(tabEmpty + it % C::TAB_SLOTS);
+        tw::mbar_arrive(tabEmpty + tsl);
+        if (++tsl == C::TAB_SLOTS) { tsl = 0; tph ^= 1; }
       }
     }
   } else if (warp >= C::FIRST_EPI_WARP) {
     // ------------------------------------------------------------------ epilogue
     const int quad = warp & 3;                              // TMEM lane quadrant this warp may read
     const int group = (warp - C::FIRST_EPI_WARP) >> 2;      // column group
+    const float alpha = __ldg(p.alpha);
     uint32_t it = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
+    for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++it) {
       const int mbi = tile / p.tiles_n, nt = tile % p.tiles_n;
       const uint32_t stage = it % C::ACC_STAGES, aph = (it / C::ACC_STAGES) & 1;
-      ok = tw::mbar_wait(accFull + stage, aph, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      if (!tw::mbar_wait_warp(accFull + stage, aph, abort_flag)) break;
       tw::tc_fence_after();
-      const float alpha = __ldg(p.alpha);
       const uint32_t t_base = tmem + ((uint32_t)(quad * 32) << 16) + C::TM_ACC + stage * BN + group * C::EPI_COLS;
-      uint32_t packed[C::EPI_COLS / 2];
+      // drain this warp's slab with back-to-back loads and one wait, then hand the TMEM stage back
+      uint32_t r[C::EPI_COLS / 32][32];
 #pragma unroll
-      for (int part = 0; part < C::EPI_COLS / 32; ++part) {
-        uint32_t r[32];
-        tw::tmem_load_32x32(t_base + part * 32, r);
-        tw::tmem_load_wait();
-#pragma unroll
-        for (int q = 0; q < 16; ++q) {
-          __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[2 * q]) * alpha, __uint_as_float(r[2 * q + 1]) * alpha);
-          packed[part * 16 + q] = *reinterpret_cast<uint32_t*>(&b);
-        }
-      }
-      // accumulator drained into registers: hand the TMEM stage back before storing
+      for (int part = 0; part < C::EPI_COLS / 32; ++part) tw::tmem_load_32x32(t_base + part * 32, r[part]);
+      tw::tmem_load_wait();
       tw::tc_fence_before();
       __syncwarp();
       if (lane == 0) tw::mbar_arrive(accEmpty + stage);
       const int row = mbi * 128 + quad * 32 + lane;
       const int col = nt * BN + group * C::EPI_COLS;
+#ifdef TW_EXP_NOSTORE
+      if (row < 0) {
+#else
       if (row < p.m && col < p.n) {
-        uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)row * p.n + col);
+#endif
+        __nv_bfloat16* dst = p.out + (size_t)row * p.n + col;
 #pragma unroll
-        for (int j = 0; j < C::EPI_COLS / 8; ++j)
-          dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+        for (int part = 0; part < C::EPI_COLS / 32; ++part) {
+#pragma unroll
+          for (int v = 0; v < 2; ++v) {                     // 16 columns = 32 bytes per store
+            uint32_t w[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[part][16 * v + 2 * q]) * alpha,
+                                                       __uint_as_float(r[part][16 * v + 2 * q + 1]) * alpha);
+              w[q] = *reinterpret_cast<uint32_t*>(&b);
+            }
+            tw::store_256(dst + part * 32 + v * 16, w);
+          }
+        }
       }
     }
   }
@@ -376,11 +462,11 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-bool make_map(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const cuuint64_t* dims,
-              const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swz) {
+bool make_map(CUtensorMap* map, int rank, const void* base, const cuuint64_t* dims, const cuuint64_t* strides,
+              const cuuint32_t* box, CUtensorMapSwizzle swz) {
   cuuint32_t ones[3] = {1, 1, 1};
-  return encode_fn()(map, type, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, ones,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box,
+                     ones, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -388,29 +474,28 @@ template <int BN>
 int launch(int m, int n, int k, const void* a_codes, const void* w_codes, const void* sfa, const void* sfb, void* out,
            const float* alpha, void* workspace, cudaStream_t stream, const TwRepairIO* io, int sms) {
   using C = Cfg<BN>;
-  CUtensorMap tm_a, tm_w0, tm_w1;
+  CUtensorMap tm_a0, tm_a1, tm_w0, tm_w1;
   const int planes = io->na > 0 ? 2 : 1;
   {
+    // activation codes [planes, mp, k/2]: K256 boxes for the base plane, K128 boxes for residual blocks
     cuuint64_t dims[3] = {(cuuint64_t)k / 2, (cuuint64_t)io->mp, (cuuint64_t)planes};
     cuuint64_t strides[2] = {(cuuint64_t)k / 2, (cuuint64_t)io->mp * (k / 2)};
-    cuuint32_t box[3] = {64, 128, 1};
-    if (!make_map(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a_codes, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B))
-      return TW_ERR_TENSOR_MAP;
+    cuuint32_t box0[3] = {128, 128, 1}, box1[3] = {64, 128, 1};
+    if (!make_map(&tm_a0, 3, a_codes, dims, strides, box0, CU_TENSOR_MAP_SWIZZLE_128B)) return TW_ERR_TENSOR_MAP;
+    if (!make_map(&tm_a1, 3, a_codes, dims, strides, box1, CU_TENSOR_MAP_SWIZZLE_64B)) return TW_ERR_TENSOR_MAP;
   }
   {
     cuuint64_t dims[2] = {(cuuint64_t)k / 2, (cuuint64_t)n};
     cuuint64_t strides[1] = {(cuuint64_t)k / 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)(n >= BN ? BN : 128)};
-    if (!make_map(&tm_w0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w_codes, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B))
-      return TW_ERR_TENSOR_MAP;
+    cuuint32_t box[2] = {128, (cuuint32_t)BN};
+    if (!make_map(&tm_w0, 2, w_codes, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return TW_ERR_TENSOR_MAP;
   }
   {
     const bool has = io->hasw != 0;
     cuuint64_t dims[2] = {64, (cuuint64_t)(has ? (size_t)io->bank_blocks * 128 : 128)};
     cuuint64_t strides[1] = {64};
     cuuint32_t box[2] = {64, 128};
-    if (!make_map(&tm_w1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, has ? (const void*)io->wr : w_codes, dims, strides, box,
-                  CU_TENSOR_MAP_SWIZZLE_64B))
+    if (!make_map(&tm_w1, 2, has ? (const void*)io->wr : w_codes, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B))
       return TW_ERR_TENSOR_MAP;
   }
   Params p{};
@@ -434,7 +519,7 @@ int launch(int m, int n, int k, const void* a_codes, const void* w_codes, const 
     configured = true;
   }
   const int grid = p.tiles < sms ? p.tiles : sms;
-  fused_kernel<BN><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tm_a, tm_w0, tm_w1, p);
+  fused_kernel<BN><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tm_a0, tm_a1, tm_w0, tm_w1, p);
   return cudaGetLastError() == cudaSuccess ? TW_OK : TW_ERR_LAUNCH;
 }
 
@@ -448,7 +533,8 @@ extern "C" int tw_fused(int m, int n, int k, const void* a_codes, const void* w_
                         void* out, const float* alpha, void* workspace, void* stream, const TwRepairIO* io) {
   if (!io || !a_codes || !w_codes || !sfa || !sfb || !out || !alpha || !workspace) return TW_ERR_ARGUMENT;
   if (m <= 0 || n <= 0 || k <= 0) return TW_ERR_ARGUMENT;
-  if (n % 128 || k % 128 || k / 128 > KB_MAX) return TW_ERR_SHAPE;
+  if (n % 128 || k % 128) return TW_ERR_SHAPE;
+  if (k / 128 > KB_MAX) return TW_ERR_TOO_LARGE;
   if (io->m != m || io->n != n || io->k != k || io->mp != (m + 15) / 16 * 16) return TW_ERR_SHAPE;
   if (io->na < 0 || io->na > k / 128) return TW_ERR_ARGUMENT;
   if (io->na > 0 && !io->a1s_swz) return TW_ERR_MISSING_SWIZZLED;
