@@ -14,10 +14,11 @@
 //
 // CTA = one 128 x BN output tile at a time (persistent over tiles), warp-specialised:
 //   warp 0      producer of base stages (TMA, 128-byte swizzle; bulk copies of scale atoms)
-//   warp 1      MMA issuer: scale atoms smem -> TMEM (tcgen05.cp), MMAs, commits
+//   warp 1      MMA issuer: MMAs, scale copies of repair units, commits
 //   warp 2      producer of repair units (TMA, 64-byte swizzle)
 //   warp 3      builds the per-tile term tables (A-support bits, W1 bank positions) ahead of use
-//   warps 4-11  epilogue: TMEM -> registers -> bf16 -> global (16-byte stores), TMEM released first
+//   warps 4,5   copy the base-stage scale atoms smem -> TMEM (tcgen05.cp) ahead of the MMA issuer
+//   warps 8-15  epilogue: TMEM -> registers -> bf16 -> global (32-byte stores)
 // No cluster, no multicast.
 #include <cuda.h>
 #include "tw_common.cuh"
@@ -37,7 +38,8 @@ template <int BN> struct Cfg {
   static constexpr int TAB_SLOTS = 3;                         // per-tile term tables built ahead
   static constexpr int ACC_STAGES = BN == 256 ? 1 : 2;
   static constexpr int EPI_WARPS = 8;
-  static constexpr int FIRST_EPI_WARP = 4;
+  static constexpr int FIRST_EPI_WARP = 8;                    // warps 0-3 and 4-5 are single-thread roles, 6-7 idle
+  static constexpr int SF_THREADS = 2;                        // threads that copy base-stage scales into TMEM
   static constexpr int EPI_GROUPS = EPI_WARPS / 4;            // column groups per lane quadrant
   static constexpr int EPI_COLS = BN / EPI_GROUPS;            // columns per epilogue warp
   static constexpr int THREADS = (FIRST_EPI_WARP + EPI_WARPS) * 32;
@@ -55,16 +57,16 @@ template <int BN> struct Cfg {
   static constexpr int OFF_TAB = OFF_SFW1 + W1_SLOTS * SF_ATOM;
   static constexpr int TAB_BYTES = HALVES * KB_MAX * 4 + (HALVES + 1) * (KB_MAX / 32) * 4;
   static constexpr int OFF_BAR = OFF_TAB + TAB_SLOTS * TAB_BYTES;
-  static constexpr int NUM_BARS = 2 * STAGES + 2 * A1_SLOTS + 2 * W1_SLOTS + 2 * TAB_SLOTS + 2 * ACC_STAGES;
+  static constexpr int NUM_BARS = 2 * STAGES + 2 * A1_SLOTS + 2 * W1_SLOTS + 2 * TAB_SLOTS + 2 * ACC_STAGES + 4 + A1_SLOTS + W1_SLOTS;
   static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 64 + 1024;  // + alignment slack
   // tensor-memory columns: accumulators, then double-buffered scale regions
   static constexpr int TM_ACC = 0;
   static constexpr int TM_SFA0 = ACC_STAGES * BN;                        // 2 x 16 columns
   static constexpr int TM_SFB0 = TM_SFA0 + 32;                           // 2 x 16*HALVES columns
-  static constexpr int TM_SFA1 = TM_SFB0 + 32 * HALVES;                  // 2 x 2 x 8 columns (two units per step)
-  static constexpr int TM_SFW1 = TM_SFA1 + 32;                           // 2 x 8 columns
+  static constexpr int TM_SFA1 = TM_SFB0 + 32 * HALVES;                  // 8 columns per A1 slot
+  static constexpr int TM_SFW1 = TM_SFA1 + 32;                           // 8 columns per W1 slot
   static constexpr int TM_COLS = 512;
-  static_assert(TM_SFW1 + 16 <= TM_COLS, "tensor memory budget");
+  static_assert(A1_SLOTS * 8 <= 32 && TM_SFW1 + 8 * W1_SLOTS <= TM_COLS, "tensor memory budget");
 };
 static_assert(Cfg<256>::SMEM_BYTES <= 232448 && Cfg<128>::SMEM_BYTES <= 232448, "shared memory budget");
 
@@ -146,7 +148,11 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
   uint64_t* tabEmpty = tabFull + C::TAB_SLOTS;
   uint64_t* accFull = tabEmpty + C::TAB_SLOTS;
   uint64_t* accEmpty = accFull + C::ACC_STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accEmpty + C::ACC_STAGES);
+  uint64_t* sfFull = accEmpty + C::ACC_STAGES;   // base-stage scales resident in TMEM region [step parity]
+  uint64_t* sfEmpty = sfFull + 2;
+  uint64_t* usfA = sfEmpty + 2;                  // scales of the A1 unit in slot i are in TMEM
+  uint64_t* usfW = usfA + C::A1_SLOTS;           // same for W1 units
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(usfW + C::W1_SLOTS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   auto table = [&](uint32_t i) -> TermTable<BN>& {
     return *reinterpret_cast<TermTable<BN>*>(smem + C::OFF_TAB + (i % C::TAB_SLOTS) * C::TAB_BYTES);
@@ -159,8 +165,11 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
     for (int i = 0; i < C::STAGES; ++i) { tw::mbar_init(fullS + i, 1); tw::mbar_init(emptyS + i, 1); }
     for (int i = 0; i < C::A1_SLOTS; ++i) { tw::mbar_init(fullA1 + i, 1); tw::mbar_init(emptyA1 + i, 1); }
     for (int i = 0; i < C::W1_SLOTS; ++i) { tw::mbar_init(fullW1 + i, 1); tw::mbar_init(emptyW1 + i, 1); }
-    for (int i = 0; i < C::TAB_SLOTS; ++i) { tw::mbar_init(tabFull + i, 1); tw::mbar_init(tabEmpty + i, 2); }
+    for (int i = 0; i < C::TAB_SLOTS; ++i) { tw::mbar_init(tabFull + i, 1); tw::mbar_init(tabEmpty + i, 2 + C::SF_THREADS); }
     for (int i = 0; i < C::ACC_STAGES; ++i) { tw::mbar_init(accFull + i, 1); tw::mbar_init(accEmpty + i, C::EPI_WARPS); }
+    for (int i = 0; i < 2; ++i) { tw::mbar_init(sfFull + i, C::SF_THREADS); tw::mbar_init(sfEmpty + i, 1); }
+    for (int i = 0; i < C::A1_SLOTS; ++i) tw::mbar_init(usfA + i, 1);
+    for (int i = 0; i < C::W1_SLOTS; ++i) tw::mbar_init(usfW + i, 1);
     *abort_flag = 0;
     tw::fence_barrier_init();
     tw::tma_prefetch_desc(&tm_a0); tw::tma_prefetch_desc(&tm_a1);
@@ -268,11 +277,10 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
       constexpr uint64_t DSF = (uint64_t(1) << 46) | (uint64_t(128 >> 4) << 32);
       const uint32_t smem_u = tw::smem_u32(smem);
       const uint32_t a0_base = (smem_u + C::OFF_A0) >> 4, w0_base = (smem_u + C::OFF_W0) >> 4;
-      const uint32_t sf0_base = (smem_u + C::OFF_SF0) >> 4;
       const uint32_t a1_base = (smem_u + C::OFF_A1) >> 4, w1_base = (smem_u + C::OFF_W1) >> 4;
-      const uint32_t sfa1_base = (smem_u + C::OFF_SFA1) >> 4, sfw1_base = (smem_u + C::OFF_SFW1) >> 4;
       const uint32_t t_sfa0_b = tmem + C::TM_SFA0, t_sfb0_b = tmem + C::TM_SFB0;
       uint32_t s = 0, ph = 0;                  // base stage slot / phase
+      uint32_t sfp = 0, sfph = 0;              // TMEM scale region (step parity) / its barrier phase
       uint32_t sa = 0, pa = 0, sw = 0, pw = 0; // unit slots / phases
       uint32_t it = 0, tsl = 0, tph = 0;       // tile counter, table slot / phase
       for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
@@ -293,28 +301,12 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
 #pragma unroll
             for (int h = 0; h < C::HALVES; ++h) wbits[h] = tab.w1bits[h][kb0 >> 5];
           }
-          ok = tw::mbar_wait(fullS + s, ph, abort_flag);
+          // the scale-copy threads waited for the stage's data and moved its scales into TMEM
+          ok = tw::mbar_wait(sfFull + sfp, sfph, abort_flag) && tw::mbar_wait(fullS + s, ph, abort_flag);
           if (!ok) break;
-          tw::tc_fence_after_load();
+          tw::tc_fence_after();
           const uint32_t a0_lo = a0_base + s * (C::A0_TILE >> 4), w0_lo = w0_base + s * (C::W0_TILE >> 4);
-          const uint32_t sf_lo = sf0_base + s * (C::STAGE_SF >> 4);
-#ifdef TW_EXP_DB
-          const uint32_t t_sfa0 = t_sfa0_b + (st & 1) * 16, t_sfb0 = t_sfb0_b + (st & 1) * 16 * C::HALVES;
-#else
-          const uint32_t t_sfa0 = t_sfa0_b, t_sfb0 = t_sfb0_b;
-#endif
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {                            // scales of the q-th K64 slice into TMEM
-            if (q < nq) {
-              tw::tc_copy_scales(t_sfa0 + 4 * q, DSF | (sf_lo + q * 32));
-#ifndef TW_EXP_SFA_ONLY
-#pragma unroll
-              for (int h = 0; h < C::HALVES; ++h)
-                if (h * 128 < n_rows)
-                  tw::tc_copy_scales(t_sfb0 + 4 * C::HALVES * q + 4 * h, DSF | (sf_lo + (1 + h) * 128 + q * 32));
-#endif
-            }
-          }
+          const uint32_t t_sfa0 = t_sfa0_b + sfp * 16, t_sfb0 = t_sfb0_b + sfp * 16 * C::HALVES;
 #pragma unroll
           for (int q = 0; q < 4; ++q)                              // A0 W0
             if (q < nq)
@@ -330,15 +322,12 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
               if (!((ab >> j) & 1u) || !ok) continue;
-              ok = tw::mbar_wait(fullA1 + sa, pa, abort_flag);
+              ok = tw::mbar_wait(usfA + sa, pa, abort_flag);       // data landed and its scales are in TMEM
               if (!ok) continue;
-              tw::tc_fence_after_load();
+              tw::tc_fence_after();
               a1_lo[j] = a1_base + sa * (UNIT_TILE >> 4);
               a1_bar[j] = sa;
-              const uint32_t sfa1_lo = sfa1_base + sa * (SF_ATOM >> 4);
-              const uint32_t t_sfa1 = tmem + C::TM_SFA1 + j * 8;
-#pragma unroll
-              for (int c = 0; c < 2; ++c) tw::tc_copy_scales(t_sfa1 + 4 * c, DSF | (sfa1_lo + c * 32));
+              const uint32_t t_sfa1 = tmem + C::TM_SFA1 + sa * 8;
 #pragma unroll
               for (int c = 0; c < 2; ++c)
                 tw::tc_mma_nvf4(acc, D64 | (a1_lo[j] + 2 * c), D128 | (w0_lo + 4 * j + 2 * c), idesc_base,
@@ -352,19 +341,17 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
 #pragma unroll
               for (int h = 0; h < C::HALVES; ++h) {
                 if (!((wb >> (2 * h + j)) & 1u) || !ok) continue;
-                ok = tw::mbar_wait(fullW1 + sw, pw, abort_flag);
+                ok = tw::mbar_wait(usfW + sw, pw, abort_flag);
                 if (!ok) continue;
-                tw::tc_fence_after_load();
-                const uint32_t w1_lo = w1_base + sw * (UNIT_TILE >> 4), sfw1_lo = sfw1_base + sw * (SF_ATOM >> 4);
-                const uint32_t t_sfw1 = tmem + C::TM_SFW1;
-#pragma unroll
-                for (int c = 0; c < 2; ++c) tw::tc_copy_scales(t_sfw1 + 4 * c, DSF | (sfw1_lo + c * 32));
+                tw::tc_fence_after();
+                const uint32_t w1_lo = w1_base + sw * (UNIT_TILE >> 4);
+                const uint32_t t_sfw1 = tmem + C::TM_SFW1 + sw * 8;
 #pragma unroll
                 for (int c = 0; c < 2; ++c)
                   tw::tc_mma_nvf4(acc + h * 128, D128 | (a0_lo + 4 * j + 2 * c), D64 | (w1_lo + 2 * c), IDESC_128,
                                   t_sfa0 + 4 * (2 * j + c), t_sfw1 + 4 * c, 1u);
                 if (p.cross && ((ab >> j) & 1u)) {
-                  const uint32_t t_sfa1 = tmem + C::TM_SFA1 + j * 8;
+                  const uint32_t t_sfa1 = tmem + C::TM_SFA1 + a1_bar[j] * 8;
 #pragma unroll
                   for (int c = 0; c < 2; ++c)
                     tw::tc_mma_nvf4(acc + h * 128, D64 | (a1_lo[j] + 2 * c), D64 | (w1_lo + 2 * c), IDESC_128,
@@ -381,7 +368,9 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
             }
           }
           tw::tc_commit(emptyS + s);
+          tw::tc_commit(sfEmpty + sfp);
           if (++s == C::STAGES) { s = 0; ph ^= 1; }
+          if (++sfp == 2) { sfp = 0; sfph ^= 1; }
           abits >>= 2;
 #pragma unroll
           for (int h = 0; h < C::HALVES; ++h) wbits[h] >>= 2;
@@ -389,6 +378,79 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
         if (ok) tw::tc_commit(accFull + stage);
         tw::mbar_arrive(tabEmpty + tsl);
         if (++tsl == C::TAB_SLOTS) { tsl = 0; tph ^= 1; }
+      }
+    }
+  } else if (warp == 4 || warp == 5) {
+    // ------------------------------------------------------------------ scale copies smem -> TMEM
+    // Issuing a tcgen05.cp costs its thread tens of cycles and a K256 step needs 4 * (1 + BN/128)
+    // of them plus two per repair unit, so they are issued by two threads of their own instead of
+    // the MMA issuer: thread 0 takes K64 slices {0,1} of the base stage and the A1 units, thread 1
+    // slices {2,3} and the W1 units. Base-stage TMEM regions are double-buffered by step parity;
+    // a unit's region belongs to its smem slot and is free again whenever that slot was reloaded.
+    if (lane == 0) {
+      const int c = warp - 4;
+      constexpr uint64_t DSF = (uint64_t(1) << 46) | (uint64_t(128 >> 4) << 32);
+      const uint32_t smem_u = tw::smem_u32(smem);
+      const uint32_t sf0_base = (smem_u + C::OFF_SF0) >> 4;
+      const uint32_t usf_base = (smem_u + (c == 0 ? C::OFF_SFA1 : C::OFF_SFW1)) >> 4;
+      const uint32_t t_usf = tmem + (c == 0 ? C::TM_SFA1 : C::TM_SFW1);
+      uint64_t* const unit_full = c == 0 ? fullA1 : fullW1;
+      uint64_t* const unit_ready = c == 0 ? usfA : usfW;
+      const uint32_t unit_slots = c == 0 ? C::A1_SLOTS : C::W1_SLOTS;
+      uint32_t s = 0, ph = 0, sfp = 0, sfph = 0, su = 0, pu = 0, it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
+        const int n_rows = min(BN, p.n - (tile % p.tiles_n) * BN);
+        const TermTable<BN>& tab = table(it);
+        ok = tw::mbar_wait(tabFull + it % C::TAB_SLOTS, (it / C::TAB_SLOTS) & 1, abort_flag);
+        uint32_t bits[C::HALVES] = {};
+        for (int st = 0; st < steps && ok; ++st) {
+          const int kb0 = 2 * st, nq = p.kb - kb0 >= 2 ? 4 : 2;
+          if ((kb0 & 31) == 0) {
+            if (c == 0) bits[0] = tab.a1bits[kb0 >> 5];
+            else {
+#pragma unroll
+              for (int h = 0; h < C::HALVES; ++h) bits[h] = tab.w1bits[h][kb0 >> 5];
+            }
+          }
+          ok = tw::mbar_wait(fullS + s, ph, abort_flag) && tw::mbar_wait(sfEmpty + sfp, sfph ^ 1, abort_flag);
+          if (!ok) break;
+          const uint32_t sf_lo = sf0_base + s * (C::STAGE_SF >> 4);
+          const uint32_t t_sfa0 = tmem + C::TM_SFA0 + sfp * 16, t_sfb0 = tmem + C::TM_SFB0 + sfp * 16 * C::HALVES;
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const int q = 2 * c + i;
+            if (q < nq) {
+              tw::tc_copy_scales(t_sfa0 + 4 * q, DSF | (sf_lo + q * 32));
+#pragma unroll
+              for (int h = 0; h < C::HALVES; ++h)
+                if (h * 128 < n_rows)
+                  tw::tc_copy_scales(t_sfb0 + 4 * C::HALVES * q + 4 * h, DSF | (sf_lo + (1 + h) * 128 + q * 32));
+            }
+          }
+          tw::tc_commit(sfFull + sfp);
+          if (++s == C::STAGES) { s = 0; ph ^= 1; }
+          if (++sfp == 2) { sfp = 0; sfph ^= 1; }
+          // units of this step, in the order the MMA issuer consumes them
+          int count = 0;
+          if (c == 0) count = __popc(bits[0] & 3u);
+          else {
+#pragma unroll
+            for (int h = 0; h < C::HALVES; ++h) count += __popc(bits[h] & 3u);
+          }
+          for (int u = 0; u < count && ok; ++u) {
+            ok = tw::mbar_wait(unit_full + su, pu, abort_flag);
+            if (!ok) break;
+            const uint32_t lo = usf_base + su * (SF_ATOM >> 4);
+            tw::tc_copy_scales(t_usf + su * 8, DSF | lo);
+            tw::tc_copy_scales(t_usf + su * 8 + 4, DSF | (lo + 32));
+            tw::tc_commit(unit_ready + su);
+            if (++su == unit_slots) { su = 0; pu ^= 1; }
+          }
+#pragma unroll
+          for (int h = 0; h < C::HALVES; ++h) bits[h] >>= 2;
+        }
+        tw::mbar_arrive(tabEmpty + it % C::TAB_SLOTS);
       }
     }
   } else if (warp >= C::FIRST_EPI_WARP) {
@@ -403,34 +465,41 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
       if (!tw::mbar_wait_warp(accFull + stage, aph, abort_flag)) break;
       tw::tc_fence_after();
       const uint32_t t_base = tmem + ((uint32_t)(quad * 32) << 16) + C::TM_ACC + stage * BN + group * C::EPI_COLS;
-      // drain this warp's slab with back-to-back loads and one wait, then hand the TMEM stage back
-      uint32_t r[C::EPI_COLS / 32][32];
-#pragma unroll
-      for (int part = 0; part < C::EPI_COLS / 32; ++part) tw::tmem_load_32x32(t_base + part * 32, r[part]);
-      tw::tmem_load_wait();
-      tw::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) tw::mbar_arrive(accEmpty + stage);
       const int row = mbi * 128 + quad * 32 + lane;
       const int col = nt * BN + group * C::EPI_COLS;
+      __nv_bfloat16* dst = p.out + (size_t)row * p.n + col;
 #ifdef TW_EXP_NOSTORE
-      if (row < 0) {
+      const bool store = row < 0;
 #else
-      if (row < p.m && col < p.n) {
+      const bool store = row < p.m && col < p.n;
 #endif
-        __nv_bfloat16* dst = p.out + (size_t)row * p.n + col;
+      // 64 columns per round: two back-to-back TMEM loads, one wait; the TMEM stage is handed back
+      // after the last round's loads, before that round is converted and stored
 #pragma unroll
-        for (int part = 0; part < C::EPI_COLS / 32; ++part) {
+      for (int round = 0; round < C::EPI_COLS / 64; ++round) {
+        uint32_t r[2][32];
+        tw::tmem_load_32x32(t_base + round * 64, r[0]);
+        tw::tmem_load_32x32(t_base + round * 64 + 32, r[1]);
+        tw::tmem_load_wait();
+        if (round == C::EPI_COLS / 64 - 1) {
+          tw::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) tw::mbar_arrive(accEmpty + stage);
+        }
+        if (store) {
 #pragma unroll
-          for (int v = 0; v < 2; ++v) {                     // 16 columns = 32 bytes per store
-            uint32_t w[8];
+          for (int part = 0; part < 2; ++part) {
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[part][16 * v + 2 * q]) * alpha,
-                                                       __uint_as_float(r[part][16 * v + 2 * q + 1]) * alpha);
-              w[q] = *reinterpret_cast<uint32_t*>(&b);
+            for (int v = 0; v < 2; ++v) {                   // 16 columns = 32 bytes per store
+              uint32_t w[8];
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[part][16 * v + 2 * q]) * alpha,
+                                                          __uint_as_float(r[part][16 * v + 2 * q + 1]) * alpha);
+                w[q] = *reinterpret_cast<uint32_t*>(&b2);
+              }
+              tw::store_256(dst + round * 64 + part * 32 + v * 16, w);
             }
-            tw::store_256(dst + part * 32 + v * 16, w);
           }
         }
       }
