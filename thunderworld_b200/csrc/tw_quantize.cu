@@ -61,6 +61,24 @@ __global__ void __launch_bounds__(256) amax_kernel(const uint4* __restrict__ x, 
   if ((threadIdx.x & 31) == 0 && peak > 0.f) atomicMax(out, __float_as_uint(peak));
 }
 
+// Correctly rounded a / b from r = RN(1 / b): q0 = RN(a r), e = a - b q0 (exact in an FMA),
+// q = RN(q0 + e r). For every divisor that is an E4M3 value this equals IEEE division for all
+// float32 numerators (tests/exact_division_check.c enumerates every mantissa pair); for the tensor
+// factor the kernel checks the 128 possible bf16 numerator mantissas itself before relying on it.
+// The sign of a zero numerator is restored (the FMA chain turns -0 into +0).
+__device__ __forceinline__ float div_by(float a, float b, float r) {
+  float q0 = __fmul_rn(a, r);
+  float e = __fmaf_rn(-b, q0, a);
+  float q = __fmaf_rn(e, r, q0);
+  return __uint_as_float(__float_as_uint(q) | (__float_as_uint(a) & 0x80000000u));
+}
+// The two values of one code byte (low nibble first) as floats, exact.
+__device__ __forceinline__ float2 e2m1x2_values(uint32_t byte) {
+  uint32_t h2;
+  asm("{ .reg .b8 t; cvt.u8.u32 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(h2) : "r"(byte));
+  return __half22float2(*reinterpret_cast<__half2*>(&h2));
+}
+
 // One group of 16 values: scale byte + 8 code bytes; optionally the dequantized values.
 __device__ __forceinline__ uint32_t encode_group(const float (&z)[16], float multiplier, uint2& codes,
                                                  float& scale_value) {
@@ -71,10 +89,11 @@ __device__ __forceinline__ uint32_t encode_group(const float (&z)[16], float mul
   raw = fminf(fmaxf(raw, 0.001953125f), 448.f);
   uint32_t sb = tw::f32_to_e4m3(raw);
   float s = tw::e4m3_to_f32(sb);
+  const float rs = __frcp_rn(s);
   uint32_t w[2] = {0u, 0u};
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    uint32_t b = tw::f32x2_to_e2m1x2(__fdiv_rn(z[2 * i], s), __fdiv_rn(z[2 * i + 1], s));
+    uint32_t b = tw::f32x2_to_e2m1x2(div_by(z[2 * i], s, rs), div_by(z[2 * i + 1], s, rs));
     w[i >> 2] |= b << (8 * (i & 3));
   }
   codes = make_uint2(w[0], w[1]);
@@ -95,6 +114,14 @@ __global__ void __launch_bounds__(PACK_THREADS) pack_kernel(PackParams p) {
   const int t = threadIdx.x, cg = t & 7, r0 = t >> 3;
   const int col = kb * TILE + cg * 16;
   const float f = load_factor(p);
+  const float rf = __frcp_rn(f);
+  // may the reciprocal sequence replace IEEE division by f? every bf16 numerator mantissa is tried
+  int fast_ok = f > 8.6736174e-19f && f < 1.1529215e18f;        // 2^-60 .. 2^60: no under/overflow inside
+  {
+    const float a = __uint_as_float(0x3f800000u | ((uint32_t)(t & 127) << 16));
+    fast_ok = fast_ok && (div_by(a, f, rf) == __fdiv_rn(a, f));
+  }
+  const bool fast = __syncthreads_and(fast_ok) != 0;
   const int kbn = p.k / TILE;
   const int cols16 = p.k / 16;
   const bool planes2 = p.repair != 0;
@@ -132,7 +159,7 @@ __global__ void __launch_bounds__(PACK_THREADS) pack_kernel(PackParams p) {
     }
     float z[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) z[i] = __fdiv_rn(y[i], f);
+    for (int i = 0; i < 16; ++i) z[i] = fast ? div_by(y[i], f, rf) : __fdiv_rn(y[i], f);
     uint2 c0, c1 = make_uint2(0u, 0u);
     float s0, s1;
     uint32_t sb0 = encode_group(z, p.base, c0, s0), sb1 = 0u;
@@ -140,13 +167,16 @@ __global__ void __launch_bounds__(PACK_THREADS) pack_kernel(PackParams p) {
       float r[16];
       const uint32_t w[2] = {c0.x, c0.y};
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        uint32_t code = (w[i >> 3] >> (4 * (i & 7))) & 15u;
-        float deq = __fmul_rn(tw::e2m1_value(code), s0);
-        r[i] = __fsub_rn(z[i], deq);
+      for (int i = 0; i < 8; ++i) {
+        const float2 val = e2m1x2_values((w[i >> 2] >> (8 * (i & 3))) & 0xffu);
+        // the product value * scale is exact in float32, so one FMA equals multiply-then-subtract
+        r[2 * i] = __fmaf_rn(-val.x, s0, z[2 * i]);
+        r[2 * i + 1] = __fmaf_rn(-val.y, s0, z[2 * i + 1]);
         if (p.repair == 3) {
-          float e = __fsub_rn(y[i], __fmul_rn(deq, f));
-          score = __fadd_rn(score, __fmul_rn(__fmul_rn(e, e), sens[i]));
+          // selector energy in the normalised domain: sum r^2 * sens (the common factor f^2 of the
+          // unnormalised residual does not change the ranking or the energy-prefix ratio)
+          score = __fmaf_rn(__fmul_rn(r[2 * i], r[2 * i]), sens[2 * i], score);
+          score = __fmaf_rn(__fmul_rn(r[2 * i + 1], r[2 * i + 1]), sens[2 * i + 1], score);
         }
       }
       if (active) {
