@@ -4,6 +4,7 @@
 // the block-scaled MMA reads. Arithmetic follows the reference encoder operation by operation
 // (thunderworld_fp4/cosmos/calibration.py:30-54, _quantize.py:81-107, _calibrated.py:11-38):
 // IEEE fp32 division, E4M3 and E2M1 round-to-nearest-even, residual taken from the rounded base.
+#include <type_traits>
 #include "tw_common.cuh"
 #include "../../include/twb200.h"
 
@@ -107,8 +108,8 @@ __device__ __forceinline__ uint32_t scale_offset(int row, int col, int cols) {
 }
 
 // grid (K/128, ceil(M/128)); each CTA packs one 128x128 tile of the lattice.
-template <bool PRESCALE>
-__global__ void __launch_bounds__(PACK_THREADS) pack_kernel(PackParams p) {
+template <bool PRESCALE, int REPAIR>
+__global__ void __launch_bounds__(PACK_THREADS, 4) pack_kernel(PackParams p) {
   __shared__ float warp_scores[PACK_THREADS / 32];
   const int kb = blockIdx.x, mbi = blockIdx.y;
   const int t = threadIdx.x, cg = t & 7, r0 = t >> 3;
@@ -124,25 +125,39 @@ __global__ void __launch_bounds__(PACK_THREADS) pack_kernel(PackParams p) {
   const bool fast = __syncthreads_and(fast_ok) != 0;
   const int kbn = p.k / TILE;
   const int cols16 = p.k / 16;
-  const bool planes2 = p.repair != 0;
-  const bool active = p.repair != 2 || p.mask[mbi * kbn + kb] != 0;
+  constexpr bool planes2 = REPAIR != 0;
+  const bool active = REPAIR != 2 || p.mask[mbi * kbn + kb] != 0;
   float dsc[16], sens[16];
   if (PRESCALE) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) dsc[i] = __ldg(p.prescale + col + i);
   }
-  if (p.repair == 3) {
+  if (REPAIR == 3) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) sens[i] = __ldg(p.sensitivity + col + i);
   }
   float score = 0.f;
-#pragma unroll 1
+  // all four passes' loads are issued before any arithmetic so that 128 bytes per thread are in flight
+  uint4 raw[4][2];
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const int row = mbi * TILE + pass * 32 + r0;
+    if (row < p.m) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.x + (size_t)row * p.k + col);
+      raw[pass][0] = __ldg(src);
+      raw[pass][1] = __ldg(src + 1);
+    } else {
+      raw[pass][0] = raw[pass][1] = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  auto run = [&](auto fast_tag) {
+  constexpr bool FAST = decltype(fast_tag)::value;
+#pragma unroll
   for (int pass = 0; pass < 4; ++pass) {
     const int row = mbi * TILE + pass * 32 + r0;
     float y[16];
-    if (row < p.m) {
-      const uint4* src = reinterpret_cast<const uint4*>(p.x + (size_t)row * p.k + col);
-      uint4 a = __ldg(src), b = __ldg(src + 1);
+    {
+      const uint4 a = raw[pass][0], b = raw[pass][1];
       uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -153,13 +168,10 @@ __global__ void __launch_bounds__(PACK_THREADS) pack_kernel(PackParams p) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) y[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(y[i], dsc[i])));
       }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) y[i] = 0.f;
     }
     float z[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) z[i] = fast ? div_by(y[i], f, rf) : __fdiv_rn(y[i], f);
+    for (int i = 0; i < 16; ++i) z[i] = FAST ? div_by(y[i], f, rf) : __fdiv_rn(y[i], f);
     uint2 c0, c1 = make_uint2(0u, 0u);
     float s0, s1;
     uint32_t sb0 = encode_group(z, p.base, c0, s0), sb1 = 0u;
@@ -172,7 +184,7 @@ __global__ void __launch_bounds__(PACK_THREADS) pack_kernel(PackParams p) {
         // the product value * scale is exact in float32, so one FMA equals multiply-then-subtract
         r[2 * i] = __fmaf_rn(-val.x, s0, z[2 * i]);
         r[2 * i + 1] = __fmaf_rn(-val.y, s0, z[2 * i + 1]);
-        if (p.repair == 3) {
+        if (REPAIR == 3) {
           // selector energy in the normalised domain: sum r^2 * sens (the common factor f^2 of the
           // unnormalised residual does not change the ranking or the energy-prefix ratio)
           score = __fmaf_rn(__fmul_rn(r[2 * i], r[2 * i]), sens[2 * i], score);
@@ -209,7 +221,9 @@ __global__ void __launch_bounds__(PACK_THREADS) pack_kernel(PackParams p) {
       if (planes2) *reinterpret_cast<uint32_t*>(p.scales_swz + (size_t)p.mb * 128 * cols16 + off) = lo1;
     }
   }
-  if (p.repair == 3) {
+  };
+  if (fast) run(std::true_type{}); else run(std::false_type{});
+  if (REPAIR == 3) {
 #pragma unroll
     for (int o = 16; o; o >>= 1) score = __fadd_rn(score, __shfl_xor_sync(0xffffffffu, score, o));
     if ((t & 31) == 0) warp_scores[t >> 5] = score;
@@ -305,8 +319,18 @@ extern "C" int tw_quantize(const TwQuantizeArgs* a, void* stream_) {
   p.repair = a->repair; p.factor_given = a->factor_given;
   p.base = a->base; p.res = a->res; p.gain = a->gain;
   dim3 grid(kb, mb);
-  if (a->prescale) pack_kernel<true><<<grid, PACK_THREADS, 0, stream>>>(p);
-  else pack_kernel<false><<<grid, PACK_THREADS, 0, stream>>>(p);
+  auto launch = [&](auto pre, auto mode) {
+    pack_kernel<decltype(pre)::value, decltype(mode)::value><<<grid, PACK_THREADS, 0, stream>>>(p);
+  };
+  auto by_mode = [&](auto pre) {
+    switch (a->repair) {
+      case 0: launch(pre, std::integral_constant<int, 0>{}); break;
+      case 1: launch(pre, std::integral_constant<int, 1>{}); break;
+      case 2: launch(pre, std::integral_constant<int, 2>{}); break;
+      default: launch(pre, std::integral_constant<int, 3>{}); break;
+    }
+  };
+  if (a->prescale) by_mode(std::true_type{}); else by_mode(std::false_type{});
   if (a->repair == 3) choose_kernel<<<mb, 128, kb * sizeof(float), stream>>>(scores, a->mask, kb, a->na, a->energy);
   return cudaGetLastError() == cudaSuccess ? TW_OK : TW_ERR_LAUNCH;
 }
