@@ -61,6 +61,16 @@ typedef struct TwQuantizeArgs {
 size_t tw_quantize_workspace(int m, int k);
 int tw_quantize(const TwQuantizeArgs* args, void* stream);
 
+/* tw_quantize without caller-provided scratch. No counterpart in the reference: it serves hosts that may
+ * not allocate device memory where they quantize (a plugin inside another framework's memory plan, a loop
+ * that forbids allocation after start-up). `args->workspace` is ignored; the scratch is a fixed array inside
+ * the library, one per GPU, held until the process exits. Limit: ceil(m/128) * (k/128) <=
+ * tw_quantize_static_max_tiles() (16384), larger problems return the "size exceeds the stated maximum" status.
+ * The first call on a device looks the array's address up and should come before any stream capture. All
+ * calls on a device share the array: calls that overlap on the GPU race. Allocates nothing. */
+int tw_quantize_static(const TwQuantizeArgs* args, void* stream);
+int tw_quantize_static_max_tiles(void);
+
 /* Row-major E4M3 scale bytes [rows, cols] -> atom layout [ceil(rows/128)*128, cols], padding zeroed.
  * Replaces thunderworld_fp4/cutlass/layout.py:7-25 (swizzle). cols % 4 == 0. */
 int tw_swizzle_scales(const uint8_t* src, int rows, int cols, uint8_t* dst, void* stream);
@@ -92,8 +102,8 @@ size_t tw_workspace(int m, int n, int k);
 int tw_fused(int m, int n, int k, const void* a_codes, const void* w_codes, const void* sfa_swz,
              const void* sfb_swz, void* out_bf16, const float* alpha_dev, void* workspace, void* stream,
              const TwRepairIO* io);
-/* Number of tcgen05 MMA instructions (128 x BN x 64) the last-described problem issues; host-side
- * helper for the issued-work ledger (thunderworld_fp4/cosmos/budget.py:36-67). Pure function. */
+/* N extent of the output tile the kernel uses for this n (256, or 128 when n is an odd multiple of
+ * 128). Pure host function. */
 int tw_fused_tile_n(int n);
 
 #ifdef __cplusplus

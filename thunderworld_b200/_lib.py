@@ -66,6 +66,8 @@ def load():
     lib.tw_abi_version.argtypes = []; lib.tw_abi_version.restype = _i
     lib.tw_quantize_workspace.argtypes = [_i, _i]; lib.tw_quantize_workspace.restype = ctypes.c_size_t
     lib.tw_quantize.argtypes = [ctypes.POINTER(QuantizeArgs), _vp]; lib.tw_quantize.restype = _i
+    lib.tw_quantize_static.argtypes = [ctypes.POINTER(QuantizeArgs), _vp]; lib.tw_quantize_static.restype = _i
+    lib.tw_quantize_static_max_tiles.argtypes = []; lib.tw_quantize_static_max_tiles.restype = _i
     lib.tw_swizzle_scales.argtypes = [_vp, _i, _i, _vp, _vp]; lib.tw_swizzle_scales.restype = _i
     lib.tw_workspace.argtypes = [_i] * 3; lib.tw_workspace.restype = ctypes.c_size_t
     lib.tw_fused.argtypes = [_i] * 3 + [_vp] * 8 + [ctypes.POINTER(RepairIO)]; lib.tw_fused.restype = _i
@@ -86,5 +88,6 @@ def check(status):
         raise RuntimeError(load().tw_status(status).decode())
 
 
-EXPORTS = ('tw_status', 'tw_abi_version', 'tw_quantize_workspace', 'tw_quantize', 'tw_swizzle_scales',
+EXPORTS = ('tw_status', 'tw_abi_version', 'tw_quantize_workspace', 'tw_quantize', 'tw_quantize_static',
+           'tw_quantize_static_max_tiles', 'tw_swizzle_scales',
            'tw_workspace', 'tw_fused', 'tw_fused_tile_n')

@@ -344,3 +344,44 @@ extern "C" int tw_swizzle_scales(const uint8_t* src, int rows, int cols, uint8_t
   swizzle_kernel<<<(unsigned)((work + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(src, dst, rows, cols, rp);
   return cudaGetLastError() == cudaSuccess ? TW_OK : TW_ERR_LAUNCH;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Quantizer entry point for callers that cannot allocate device memory
+// ---------------------------------------------------------------------------------------------
+// Some hosts of this library may not call cudaMalloc at the point where they quantize: a plugin
+// that runs inside another framework's memory plan, a real-time loop that forbids allocation after
+// start-up, code running while a pool is frozen. tw_quantize needs a few KB of scratch (the
+// amax word and one selector score per 128x128 lattice tile); here that scratch is a fixed array
+// in the library's own device image, so the caller passes inputs and outputs only.
+//
+// The array exists once per GPU that loads the library and stays until the process exits. Every
+// call on a device shares it and it keeps the previous call's contents: the amax word is cleared
+// at the start of each call and the scores are fully rewritten before they are read, but two calls
+// that overlap on the same GPU (different streams) race on it. The array name below is only a
+// host-side handle; the device address is looked up once per device with cudaGetSymbolAddress.
+namespace {
+constexpr int STATIC_TILES = 16384;                       // lattice tiles: ceil(m/128) * (k/128) <= 16384
+static __device__ __align__(256) unsigned char g_quantize_scratch[256 + STATIC_TILES * sizeof(float)];
+constexpr int MAX_DEVICES = 64;
+void* g_scratch_address[MAX_DEVICES] = {};
+}  // namespace
+
+extern "C" int tw_quantize_static_max_tiles(void) { return STATIC_TILES; }
+
+extern "C" int tw_quantize_static(const TwQuantizeArgs* a, void* stream) {
+  if (!a) return TW_ERR_ARGUMENT;
+  if (a->m <= 0 || a->k <= 0 || a->k % 128) return a->k % 128 ? TW_ERR_SHAPE : TW_ERR_ARGUMENT;
+  const long long tiles = (long long)((a->m + 127) / 128) * (a->k / 128);
+  if (tiles > STATIC_TILES) return TW_ERR_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return TW_ERR_LAUNCH;
+  if (!g_scratch_address[dev]) {
+    // first call on this device (it is the current one): resolve the device address of the array
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_quantize_scratch) != cudaSuccess || !ptr) return TW_ERR_LAUNCH;
+    g_scratch_address[dev] = ptr;
+  }
+  TwQuantizeArgs local = *a;
+  local.workspace = g_scratch_address[dev];
+  return tw_quantize(&local, stream);
+}
