@@ -96,6 +96,10 @@ typedef struct TwRepairIO {
   /* extensions */
   const uint8_t* a1s_swz;  /* residual-plane activation scales, atom layout [ceil(m/128)*128, k/16] */
   const uint8_t* wrs_swz;  /* W1 bank scales, atom layout per tile: [slots][1024] */
+  const void* bias;        /* optional bf16 [n]: out = bf16(alpha * acc + bias), one rounding, as the reference's
+                              FP4Linear kernel does (thunderworld_fp4/_linear_kernels.py:79-81) */
+  int32_t mask_per_n;      /* nonzero: mask is bool [ceil(m/128), n/128, k/128], one A support per output
+                              block (explicit masks of FP4Linear, thunderworld_fp4/linear.py:115-119) */
 } TwRepairIO;
 /* Bytes of caller-owned workspace (holds the device status word; zero it once). */
 size_t tw_workspace(int m, int n, int k);

@@ -1,0 +1,146 @@
+"""`RepairLinear`: the module that replaces every generation `nn.Linear` in the joint-inference runtime
+(reference: packages/fp4-repair/src/thunderworld_fp4/cosmos/linears.py:55-265). It owns the offline asset
+(W0/W1 planes, factor, prescale, tile scores, selector weights), builds one operator per
+(rows, repair spec) while the controller is warming, shares W0 between them and keeps the W1 tiles of a
+budget plan in one union bank addressed through `wloc`. The launch-table search of the reference has no
+counterpart: there is one sm_100a kernel configuration per shape.
+
+Controller protocol (duck-typed, as in the reference): `linear_spec(name, default) -> LinearSpec`,
+`warming: bool`, `record_linear(name, shape, n, spec, op)`, optional `budget_plan` (RepairPlan) and
+`config` (RunConfig: activation_repair_energy).
+"""
+import json
+import torch
+from .. import ops
+from ..linear import sampled_block_rank
+from ..native import Native, quantize_weight
+from .assets import compact, expand
+
+
+class RepairLinear(torch.nn.Module):
+    def __init__(self, source, controller, name, spec, asset=None):
+        super().__init__()
+        self.in_features, self.out_features = source.in_features, source.out_features
+        self.controller, self.name, self.default = controller, name, spec
+        self.repair_energy = getattr(getattr(controller, 'config', None), 'activation_repair_energy', 1.)
+        n, k = self.out_features, self.in_features
+        if n % 128 or k % 128:
+            raise ValueError(f'Unsupported FP4 projection {name}: {n}x{k}')
+        plan = getattr(controller, 'budget_plan', None)
+        if asset is None:
+            w = source.weight.detach().cuda().bfloat16().contiguous()
+            codes, scales, factor = quantize_weight(w)
+            # residual magnitude per tile: deterministic offline fallback score for W1 selection
+            score = scales[1].float().reshape(n // 128, 128, k // 128, 8).square().sum((1, 3))
+            asset = dict(codes=codes.cpu(), scales=scales.cpu(), factor=factor.cpu(), prescale=torch.ones(k),
+                         score=score.cpu(), bias=None if source.bias is None else source.bias.detach().cpu())
+            if plan is not None:
+                asset.update(selector='residual_sensitivity', activation_sensitivity=w.float().square().sum(0).cpu())
+        # with a plan only the union of W1 tiles any phase/branch selects is kept
+        self.weight_union = None
+        if plan is not None:
+            self.weight_union = self._plan_union(plan)
+            self.asset = compact(asset, self.weight_union)
+        else:
+            self.asset = asset
+        self.register_buffer('bias', None if asset['bias'] is None else asset['bias'].cuda().bfloat16())
+        self.register_buffer('sensitivity', asset.get('activation_sensitivity', torch.ones(k)).float().cuda())
+        self.ops, self.bound, self.weight_bank = {}, None, None
+
+    def _plan_union(self, plan):
+        return sorted(set(i for key, row in plan.linears.items() if key.split('|', 2)[-1] == self.name
+                          for i in row['w_blocks']))
+
+    def export(self):
+        return expand(self.asset, self.weight_union) if self.weight_union is not None else self.asset
+
+    def prepare_shape(self, m, spec):
+        """Build (or fetch) the operator for `m` rows under `spec`. Host work only; called while warming."""
+        key = (m, spec.key)
+        if key in self.ops:
+            self.bound = self.ops[key]
+            return
+        n, k = self.out_features, self.in_features
+        mb, kb, nb = ops.cdiv(m, 128), k // 128, n // 128
+        a = self.export()
+        c, s, g, d = (a[x].cuda() for x in ('codes', 'scales', 'factor', 'prescale'))
+        na, nw = spec.counts(n, k)
+        if self.repair_energy != 1 and 0 < na < kb and a.get('selector') != 'residual_sensitivity':
+            raise ValueError('Adaptive A repair requires an offline residual-sensitivity asset')
+        scores = a['score'].flatten()
+        if spec.weight_support is None:
+            ids = torch.argsort(scores, descending=True, stable=True)[:nw]
+        else:
+            ids = torch.tensor(spec.weight_support, dtype=torch.long)
+        if not set(a.get('mandatory_w_blocks', ())).issubset(ids.tolist()):
+            raise ValueError('Policy disables mandatory outlier W1 support')
+        selected = torch.zeros(nb * kb, dtype=torch.bool)
+        selected[ids] = True
+        wm = selected.reshape(nb, kb).repeat_interleave(128, 0).repeat_interleave(128, 1).cuda()
+        am = torch.ones((mb, k), device='cuda', dtype=torch.bool)
+        op = Native(c, s, g, d.float(), am, wm, bm=128, interleave=True, cross=spec.cross)
+        # W0 (and its atom-layout scales) is shared by every (m, A, cross) variant; W1 by equal W support
+        for (_, old_key), previous in self.ops.items():
+            for name in ('wc', 'ws', 'wg', 'd', 'ws_swz'):
+                setattr(op, name, getattr(previous, name))
+            old = json.loads(old_key)
+            same_support = old.get('weight_support') == (list(spec.weight_support) if spec.weight_support is not None else None)
+            if old['weight'] == spec.weight and same_support:
+                for name in ('wr', 'wrs', 'wi', 'off', 'wrs_swz', '_bank_key'):
+                    setattr(op, name, getattr(previous, name))
+            break
+        plan = getattr(self.controller, 'budget_plan', None)
+        if plan is not None:
+            if self.weight_bank is None:
+                union = self._plan_union(plan)
+                union_ids = torch.tensor(union, device=c.device, dtype=torch.long)
+                tiles_c = c[1].reshape(nb, 128, kb, 64).permute(0, 2, 1, 3).reshape(-1, 128, 64)
+                tiles_s = s[1].view(torch.uint8).reshape(nb, 128, kb, 8).permute(0, 2, 1, 3).reshape(-1, 128, 8)
+                self.weight_bank = (tiles_c[union_ids].contiguous(),
+                                    tiles_s[union_ids].contiguous().view(torch.float8_e4m3fn),
+                                    {v: i for i, v in enumerate(union)})
+            op.wr, op.wrs, positions = self.weight_bank
+            op.wloc = torch.tensor([positions[i] for i in sorted(ids.tolist())], device=c.device, dtype=torch.int32)
+            op.shared_bank = not op.dense_w
+            op.hasw = bool(len(ids))
+        op.na = na
+        op.weight_ids = tuple(ids.tolist())
+        op.am = op.union = torch.full((mb, kb), na == kb, device='cuda', dtype=torch.bool)
+        self.ops[key] = op
+        self.bound = op
+
+    def _compute(self, x, factor=None, packed=None):
+        op = self.bound
+        m, k = x.shape
+        kb = k // 128
+        base, res = self.asset.get('activation_scale', (1., 1.))
+        identity = bool(self.asset.get('identity_prescale', False))
+        if packed is None:
+            common = dict(wg=op.wg, base=base, res=res)
+            if self.asset.get('selector') == 'residual_sensitivity' and 0 < op.na < kb:
+                # online current-residual selection: mask written in place, then read by the GEMM
+                packed = ops.quantize(x, op.d, repair=3, na=op.na, sensitivity=self.sensitivity, mask=op.am,
+                                      factor=factor if identity else None, energy=self.repair_energy, **common)
+            else:
+                if 0 < op.na < kb:                       # sampled-energy selector of assets without sensitivities
+                    op.am.copy_(sampled_block_rank(x, op.d, m, k) < op.na)
+                mode = 0 if op.na == 0 else (1 if op.na == kb else 2)
+                use_factor = factor if (base, res) == (1., 1.) else None
+                packed = ops.quantize(x, op.d, repair=mode, mask=op.am if mode == 2 else None, factor=use_factor, **common)
+        y = op.run_packed(x, packed)
+        return y if self.bias is None else y + self.bias
+
+    def forward(self, x, *, factor=None, packed=None):
+        shape = x.shape
+        flat = x.reshape(-1, self.in_features).contiguous()
+        c = self.controller
+        spec = c.linear_spec(self.name, self.default)
+        key = (len(flat), spec.key)
+        if c.warming:
+            self.prepare_shape(len(flat), spec)
+            c.record_linear(self.name, flat.shape, self.out_features, spec, self.bound)
+        elif key not in self.ops:
+            raise RuntimeError(f'Unwarmed projection {self.name}: {key}')
+        else:
+            self.bound = self.ops[key]
+        return self._compute(flat, factor, packed).reshape(*shape[:-1], self.out_features)

@@ -78,10 +78,12 @@ struct Params {
   const int* wi; const int* off; const int* wloc;
   const uint8_t* mask;
   const float* alpha;
+  const __nv_bfloat16* bias;  // optional [n], added in fp32 before the bf16 rounding
   __nv_bfloat16* out;
   int* status;
   int m, mp, n, k, na, hasw, cross, shared, dense;
   int kb, nb, mb, tiles_n, tiles;
+  int mask_per_n;           // mask is [MB, NB, KB] (one A support per output block; 128-wide tiles only)
 };
 
 // Per-tile term table, built ahead of use by its own warp: one bit per kb for "A1 selected" and
@@ -108,7 +110,8 @@ __device__ __forceinline__ void build_table(TermTable<BN>& tab, const Params& p,
   for (int w = 0; w < words; ++w) {
     const int kb = w * 32 + lane;
     const bool in = kb < p.kb;
-    const bool sel = in && (p.na == p.kb || (p.na > 0 && p.mask[mbi * p.kb + kb] != 0));
+    const size_t mrow = p.mask_per_n ? (size_t)mbi * p.nb + nt : (size_t)mbi;
+    const bool sel = in && ((p.na == p.kb && !p.mask_per_n) || (p.na > 0 && p.mask[mrow * p.kb + kb] != 0));
     const uint32_t abits = __ballot_sync(0xffffffffu, sel);
     if (lane == 0) tab.a1bits[w] = abits;
 #pragma unroll
@@ -492,10 +495,17 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
 #pragma unroll
             for (int v = 0; v < 2; ++v) {                   // 16 columns = 32 bytes per store
               uint32_t w[8];
+              uint32_t bw[8] = {};
+              if (p.bias) {
+                const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col + round * 64 + part * 32 + v * 16);
+                const uint4 b0 = __ldg(bp), b1 = __ldg(bp + 1);
+                bw[0] = b0.x; bw[1] = b0.y; bw[2] = b0.z; bw[3] = b0.w; bw[4] = b1.x; bw[5] = b1.y; bw[6] = b1.z; bw[7] = b1.w;
+              }
 #pragma unroll
               for (int q = 0; q < 8; ++q) {
-                __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[part][16 * v + 2 * q]) * alpha,
-                                                          __uint_as_float(r[part][16 * v + 2 * q + 1]) * alpha);
+                const float lo = __fmaf_rn(__uint_as_float(r[part][16 * v + 2 * q]), alpha, tw::bf16_bits_to_float(bw[q] & 0xffffu));
+                const float hi = __fmaf_rn(__uint_as_float(r[part][16 * v + 2 * q + 1]), alpha, tw::bf16_bits_to_float(bw[q] >> 16));
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
                 w[q] = *reinterpret_cast<uint32_t*>(&b2);
               }
               tw::store_256(dst + round * 64 + part * 32 + v * 16, w);
@@ -574,10 +584,11 @@ int launch(int m, int n, int k, const void* a_codes, const void* w_codes, const 
   p.sfbw = io->wrs_swz;
   p.wi = io->wi; p.off = io->off; p.wloc = io->wloc; p.mask = io->mask;
   p.alpha = alpha;
+  p.bias = static_cast<const __nv_bfloat16*>(io->bias);
   p.out = static_cast<__nv_bfloat16*>(out);
   p.status = static_cast<int*>(workspace);
   p.m = m; p.mp = io->mp; p.n = n; p.k = k; p.na = io->na; p.hasw = io->hasw; p.cross = io->cross;
-  p.shared = io->shared; p.dense = io->dense;
+  p.shared = io->shared; p.dense = io->dense; p.mask_per_n = io->mask_per_n;
   p.kb = k / 128; p.nb = n / 128; p.mb = (m + 127) / 128;
   p.tiles_n = (n + BN - 1) / BN;
   p.tiles = p.mb * p.tiles_n;
@@ -624,6 +635,6 @@ extern "C" int tw_fused(int m, int n, int k, const void* a_codes, const void* w_
   cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
   if (major != 10) return TW_ERR_ARCH;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (n % 256 == 0) return launch<256>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms);
+  if (n % 256 == 0 && !io->mask_per_n) return launch<256>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms);
   return launch<128>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms);
 }
