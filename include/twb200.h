@@ -110,6 +110,52 @@ int tw_fused(int m, int n, int k, const void* a_codes, const void* w_codes, cons
  * 128). Pure host function. */
 int tw_fused_tile_n(int n);
 
+/* ---- streaming FP4 attention -----------------------------------------------------------------
+ * Three calls replace the reference's attention launch chain (thunderworld_fp4/runtime.py:32-108):
+ *   tw_pack_rows     pack_qk / pack_v        (_kernels.py:12-47): per-row factor max/1536, base + residual
+ *   tw_select_tiles  select_tiles[_head]     (_kernels.py:169-215): per-head quota of repaired key tiles
+ *   tw_attention     streaming_attention     (_kernels.py:51-124); no split/combine pass is needed
+ * Packed layouts: codes [planes, heads*rows_padded, 64], scales [planes, heads*rows_padded, 8] (row-major),
+ * scales_swz [planes, heads, ceil(rows_padded/128), 1024] (atom layout), factors [heads*rows_padded].
+ * Q and K rows are (head, token); V rows are (kv head, key tile, channel) with the tile's 128 tokens as
+ * columns (rows_padded = key tiles * 128). */
+typedef struct TwPackRowsArgs {
+  const void* x;                 /* bf16, element (token, head, d) at x[token*stride_row + head*stride_head + d] */
+  uint8_t *codes, *scales, *scales_swz;
+  float* factors;
+  float* energy;                 /* V only, optional: [heads, key tiles, 8] = sum x^2 / 16384 per 16 channels */
+  long long stride_row, stride_head;
+  int rows, heads, rows_padded;  /* tokens, heads, padded rows per head (16-multiple; 128-multiple for V) */
+  int repair;                    /* also emit the residual plane */
+  int transpose_v;               /* 0: Q/K packing, 1: V packing */
+  int need_energy;
+} TwPackRowsArgs;
+int tw_pack_rows(const TwPackRowsArgs* args, void* stream);
+
+typedef struct TwSelectArgs {
+  const void *q, *k;             /* bf16 inputs with the strides below */
+  const float* energy;           /* from tw_pack_rows on V */
+  int32_t *flags, *pvflags;      /* out [hq, ceil(m/128), ceil(n/128)]: `terms` where repaired, else 1 */
+  const int32_t *counts, *pvcounts; /* per query head quotas (device) */
+  long long q_stride_row, q_stride_head, k_stride_row, k_stride_head;
+  int m, n, hq, hk, terms, pv_terms;
+} TwSelectArgs;
+int tw_select_tiles(const TwSelectArgs* args, void* stream);
+
+typedef struct TwAttentionArgs {
+  const uint8_t *qc, *kc, *vc;   /* codes */
+  const uint8_t *sfq, *sfk, *sfv;/* atom-layout scales */
+  const float *qf, *kf, *vf;     /* factors */
+  const int32_t *flags, *pvflags;/* > 1 selects repair of that (head, q block, key tile); may be NULL when full / off */
+  void* out;                     /* bf16 [m, hq, 128] */
+  void* workspace;               /* tw_attention_workspace bytes; first word = device status */
+  int m, n, hq, hk, mp, np;      /* mp = ceil(m/16)*16, np = ceil(n/128)*128 */
+  int repair, full, terms;       /* QK: any repair, every tile repaired, 2/3/4 terms */
+  int pv_repair, pv_full, pv_terms;
+} TwAttentionArgs;
+size_t tw_attention_workspace(int m, int n, int hq, int hk);
+int tw_attention(const TwAttentionArgs* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -428,3 +428,33 @@ def seeded_tiles(nb, kb, fraction, seed=0):
     rng = np.random.default_rng(seed + 7919)
     count = int(round(fraction * nb * kb))
     return sorted(int(t) for t in rng.permutation(nb * kb)[:count])
+
+
+def select_tiles(q, k, v, counts, terms=3):
+    """select_tiles_head (_kernels.py:191-215): per (head, M128 block) eight sampled queries against
+    eight sampled keys of every key tile; softmax mass per tile times sqrt(V tile energy); the
+    `counts[head]` best tiles (lower index wins ties) get `terms`, the rest 1.
+    q [M,H,128], k/v [N,HK,128]; returns (flags int32 [H, MT, NT], scores float64 [H, MT, NT])."""
+    m, h = q.shape[0], q.shape[1]
+    n, hk = k.shape[0], k.shape[1]
+    mt, nt = (m + 127) // 128, (n + 127) // 128
+    flags = np.ones((h, mt, nt), np.int32)
+    scores = np.zeros((h, mt, nt))
+    keys = (np.arange(nt)[:, None] * 128 + np.arange(8)[None, :] * 16).reshape(-1)
+    for head in range(h):
+        kh = head // (h // hk)
+        vpad = np.zeros((nt * 128, 128)); vpad[:n] = v[:, kh]
+        energy = np.sqrt((vpad.reshape(nt, 128 * 128) ** 2).sum(1) / 16384.)
+        ks = k[np.minimum(keys, n - 1), kh].astype(np.float64)
+        for b in range(mt):
+            rows = np.minimum(b * 128 + np.arange(8) * 16, m - 1)
+            sim = q[rows, head].astype(np.float64) @ ks.T * 0.08838834764831845
+            sim[:, keys >= n] = -np.inf
+            w = np.exp(sim - sim.max(1, keepdims=True))
+            w /= w.sum(1, keepdims=True)
+            mass = w.reshape(8, nt, 8).sum((0, 2)) / 8.
+            sc = mass * energy
+            scores[head, b] = sc
+            order = sorted(range(nt), key=lambda j: (-sc[j], j))
+            flags[head, b, order[:counts[head]]] = terms
+    return flags, scores

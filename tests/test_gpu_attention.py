@@ -1,0 +1,122 @@
+"""GPU parity of the attention path: packed Q/K/V bytes bit-exact against the oracle's per-row
+quantizer; attention output within the reference's own tolerance (relative L2 < 0.012 against the
+decoded-FP4 streaming oracle, packages/fp4-repair/tests/test_cuda.py:12-20). P is quantized on chip
+with approximate reciprocals, as in the reference, so its codes are not bit-defined."""
+import numpy as np
+import pytest
+import torch
+from oracle import nvfp4_oracle as o
+
+pytestmark = pytest.mark.gpu
+TOL = 0.012
+
+
+def as_np(t):
+    return (t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t).cpu().numpy()
+
+
+def inputs(m=33, n=257, h=4, hk=2, seed=17):
+    g = torch.Generator().manual_seed(seed)
+    mk = lambda s, hh: (torch.randn((1, s, hh, 128), generator=g) * (torch.rand(hh, generator=g) * 1.5 + .5)[None, None, :, None])
+    return tuple(t.bfloat16().cuda() for t in (mk(m, h), mk(n, hk), mk(n, hk)))
+
+
+def rel_l2(a, b):
+    return float(np.linalg.norm(a.astype(np.float64) - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def test_pack_rows_bit_exact():
+    from thunderworld_b200.runtime import pack_inputs
+    q, k, v = inputs(m=145, n=385)
+    pq, pk, pv, mp, npad = pack_inputs(q[0], k[0], v[0], repair=True, need_energy=True, terms=3)
+    torch.cuda.synchronize()
+    assert (mp, npad) == (160, 512)
+    for packed, x, rows_padded in ((pq, q[0], mp), (pk, k[0], npad)):
+        xn = x.float().cpu().numpy()
+        for head in range(x.shape[1]):
+            xp = np.zeros((rows_padded, 128), np.float32); xp[:x.shape[0]] = xn[:, head]
+            codes, scales, factors = o.quantize_rows(xp)
+            sl = slice(head * rows_padded, (head + 1) * rows_padded)
+            assert np.array_equal(as_np(packed.codes)[:, sl], codes)
+            assert np.array_equal(as_np(packed.scales)[:, sl], scales)
+            assert np.array_equal(packed.factors.cpu().numpy()[sl], factors)
+    vn = v[0].float().cpu().numpy()
+    for head in range(v.shape[2]):
+        rows = o.pack_v_rows(vn[:, head], npad)
+        codes, scales, factors = o.quantize_rows(rows)
+        sl = slice(head * npad, (head + 1) * npad)
+        assert np.array_equal(as_np(pv.codes)[:, sl], codes)
+        assert np.array_equal(as_np(pv.scales)[:, sl], scales)
+        assert np.array_equal(pv.factors.cpu().numpy()[sl], factors)
+        # atom-layout copy of the scales, per key tile
+        for tile in range(npad // 128):
+            want = o.swizzle_scales(scales[0][tile * 128:(tile + 1) * 128]).reshape(-1)
+            assert np.array_equal(as_np(pv.scales_swz)[0, head, tile], want)
+        vp = np.zeros((npad, 128)); vp[:vn.shape[0]] = vn[:, head]
+        energy = (vp.reshape(npad // 128, 128, 8, 16) ** 2).sum((1, 3)) / 16384.
+        assert np.allclose(pv.energy.cpu().numpy()[head], energy, rtol=1e-4)
+
+
+@pytest.mark.parametrize('terms,coverage,m,n', [(3, 0., 33, 1), (2, 1., 33, 129), (3, .5, 33, 257), (4, 1., 129, 129),
+                                                (3, 1., 33, 257), (3, .5, 300, 700)])
+def test_attention_matches_oracle(terms, coverage, m, n):
+    from thunderworld_b200 import RepairConfig, fp4_attention
+    from thunderworld_b200 import ops
+    q, k, v = inputs(m=m, n=n)
+    cfg = RepairConfig(terms=terms, coverage=coverage)
+    y, mask = fp4_attention(q, k, v, cfg, return_mask=True)
+    torch.cuda.synchronize()
+    assert y.shape == q.shape and torch.isfinite(y).all()
+    flags = mask.int().cpu().numpy() * 2 + 1
+    want = o.attention_reference(q[0].float().cpu().numpy(), k[0].float().cpu().numpy(), v[0].float().cpu().numpy(), flags,
+                                 repair=coverage > 0, terms=terms)
+    err = rel_l2(y[0].float().cpu().numpy(), want)
+    assert err < TOL, err
+    if 0 < coverage < 1:
+        counts = cfg.head_counts(q.shape[2], n)
+        assert mask.sum(-1).cpu().tolist() == [[c] * mask.shape[1] for c in counts]
+
+
+def test_selector_matches_oracle_ranking():
+    from thunderworld_b200 import RepairConfig, fp4_attention
+    q, k, v = inputs(m=300, n=1500, h=4, hk=2, seed=3)
+    cfg = RepairConfig(coverage=.25, head_budgets=((0, 0.), (1, 1.), (2, .5)))
+    _, mask = fp4_attention(q, k, v, cfg, return_mask=True)
+    counts = cfg.head_counts(4, 1500)
+    want, scores = o.select_tiles(q[0].float().cpu().numpy(), k[0].float().cpu().numpy(), v[0].float().cpu().numpy(), counts)
+    got = mask.cpu().numpy()
+    assert got.sum(-1).tolist() == [[c] * 3 for c in counts]
+    diff = np.argwhere(got != (want > 1))
+    for head, b, tile in diff:                       # only ties within float32 rounding may differ
+        cut = np.sort(scores[head, b])[-counts[head]]
+        assert abs(scores[head, b, tile] - cut) <= 1e-3 * cut
+
+
+def test_explicit_mask_batch_and_graph_engine():
+    from thunderworld_b200 import FP4Attention, RepairConfig, fp4_attention, make_repair_mask
+    q, k, v = inputs(m=145, n=385)
+    cfg = RepairConfig(coverage=.5, head_budgets=((0, 0), (1, 1), (2, .25)))
+    engine = FP4Attention(cfg)
+    a, mask = engine(q, k, v, return_mask=True)
+    assert mask.sum(-1).cpu().tolist() == [[0, 0], [4, 4], [1, 1], [2, 2]]
+    old = a.clone()
+    k2, v2 = k * .7, v + 1
+    b = engine(q, k2, v2)
+    assert torch.equal(b, fp4_attention(q, k2, v2, cfg))
+    assert torch.equal(a, old) and not torch.equal(a, b)
+    explicit = make_repair_mask(145, 385, 4, {0: [(0, 3)], 2: [(1, 0), (0, 1)]}, device=q.device)
+    c, selected = engine(q, k2, v2, repair_mask=explicit, return_mask=True)
+    assert torch.equal(explicit, selected)
+    d = engine(q, k2, v2, repair_mask=explicit.logical_not())
+    assert torch.equal(d, fp4_attention(q, k2, v2, cfg, repair_mask=explicit.logical_not()))
+    assert not torch.equal(c, d)
+    engine.clear()
+    # a batch of two is two independent problems (CFG cond / uncond)
+    qb, kb, vb = (torch.cat([t, t.flip(1)]) for t in (q, k2, v2))
+    yb = fp4_attention(qb, kb, vb, cfg)
+    assert torch.equal(yb[0:1], fp4_attention(q, k2, v2, cfg))
+    assert torch.equal(yb[1:2], fp4_attention(q.flip(1), k2.flip(1), v2.flip(1), cfg))
+    with pytest.raises(ValueError):
+        fp4_attention(q[..., :64], k, v)
+    with pytest.raises(ValueError):
+        fp4_attention(q.float(), k, v)

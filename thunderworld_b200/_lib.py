@@ -30,17 +30,26 @@ class RepairIO(ctypes.Structure):
                [(n, _vp) for n in ('a1s_swz', 'wrs_swz', 'bias')] + [('mask_per_n', _i)]
 
 
-class AttentionArgs(ctypes.Structure):
-    _fields_ = [(n, _vp) for n in ('qc', 'qs', 'qf', 'kc', 'ks', 'kf', 'vc', 'vs', 'vf', 'flags', 'pvflags', 'out',
-                                   'workspace')] + \
-               [(n, _i) for n in ('m', 'n', 'hq', 'hk', 'mp', 'np', 'repair', 'full', 'terms', 'pv_repair', 'pv_full',
-                                  'pv_terms', 'batch')]
+_ll = ctypes.c_longlong
 
 
 class PackRowsArgs(ctypes.Structure):
     _fields_ = [(n, _vp) for n in ('x', 'codes', 'scales', 'scales_swz', 'factors', 'energy')] + \
-               [(n, _i) for n in ('rows', 'heads', 'stride_row', 'stride_head', 'rows_padded', 'repair', 'transpose_v',
-                                  'need_energy')]
+               [(n, _ll) for n in ('stride_row', 'stride_head')] + \
+               [(n, _i) for n in ('rows', 'heads', 'rows_padded', 'repair', 'transpose_v', 'need_energy')]
+
+
+class SelectArgs(ctypes.Structure):
+    _fields_ = [(n, _vp) for n in ('q', 'k', 'energy', 'flags', 'pvflags', 'counts', 'pvcounts')] + \
+               [(n, _ll) for n in ('q_stride_row', 'q_stride_head', 'k_stride_row', 'k_stride_head')] + \
+               [(n, _i) for n in ('m', 'n', 'hq', 'hk', 'terms', 'pv_terms')]
+
+
+class AttentionArgs(ctypes.Structure):
+    _fields_ = [(n, _vp) for n in ('qc', 'kc', 'vc', 'sfq', 'sfk', 'sfv', 'qf', 'kf', 'vf', 'flags', 'pvflags', 'out',
+                                   'workspace')] + \
+               [(n, _i) for n in ('m', 'n', 'hq', 'hk', 'mp', 'np', 'repair', 'full', 'terms', 'pv_repair', 'pv_full',
+                                  'pv_terms')]
 
 
 _lib = None
@@ -72,13 +81,10 @@ def load():
     lib.tw_workspace.argtypes = [_i] * 3; lib.tw_workspace.restype = ctypes.c_size_t
     lib.tw_fused.argtypes = [_i] * 3 + [_vp] * 8 + [ctypes.POINTER(RepairIO)]; lib.tw_fused.restype = _i
     lib.tw_fused_tile_n.argtypes = [_i]; lib.tw_fused_tile_n.restype = _i
-    for name, args in (('tw_pack_rows', [ctypes.POINTER(PackRowsArgs), _vp]),
-                       ('tw_attention', [ctypes.POINTER(AttentionArgs), _vp])):
-        if hasattr(lib, name):
-            getattr(lib, name).argtypes = args
-            getattr(lib, name).restype = _i
-    if hasattr(lib, 'tw_attention_workspace'):
-        lib.tw_attention_workspace.argtypes = [_i] * 4; lib.tw_attention_workspace.restype = ctypes.c_size_t
+    for name, args in (('tw_pack_rows', PackRowsArgs), ('tw_select_tiles', SelectArgs), ('tw_attention', AttentionArgs)):
+        getattr(lib, name).argtypes = [ctypes.POINTER(args), _vp]
+        getattr(lib, name).restype = _i
+    lib.tw_attention_workspace.argtypes = [_i] * 4; lib.tw_attention_workspace.restype = ctypes.c_size_t
     _lib = lib
     return lib
 
@@ -90,4 +96,5 @@ def check(status):
 
 EXPORTS = ('tw_status', 'tw_abi_version', 'tw_quantize_workspace', 'tw_quantize', 'tw_quantize_static',
            'tw_quantize_static_max_tiles', 'tw_swizzle_scales',
-           'tw_workspace', 'tw_fused', 'tw_fused_tile_n')
+           'tw_workspace', 'tw_fused', 'tw_fused_tile_n', 'tw_pack_rows', 'tw_select_tiles', 'tw_attention',
+           'tw_attention_workspace')
