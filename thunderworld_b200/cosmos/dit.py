@@ -1,0 +1,130 @@
+"""A DiT denoiser built from the repaired operators, for the step-level configurations: RMSNorm ->
+AdaLN modulation -> QKV (repaired linear) -> per-head RMSNorm -> FP4 attention -> out-proj -> gated
+residual -> RMSNorm -> AdaLN -> FFN-up (GELU) -> FFN-down -> gated residual.
+
+The reference runs the diffusers Cosmos3 transformer (absent here); its per-layer dataflow is the one
+spelled out in thunderworld_fp4/cosmos/ar_cache.py:72-107. Norms, modulation and GELU are plain torch
+ops; every projection is a `RepairLinear`, attention goes through the engine's `attend`.
+
+Tensor parallelism: QKV and FFN-up are column-split (heads shard with them, attention needs no
+exchange); out-proj and FFN-down are row-split, their activations are quantized under the global
+factor (4-byte MAX all-reduce) and their partial outputs summed with one all-reduce each.
+"""
+from dataclasses import dataclass
+import torch
+from .. import parallel
+from .linears import RepairLinear
+from .settings import LinearSpec
+
+
+@dataclass(frozen=True)
+class DiTConfig:
+    hidden: int = 4096
+    heads: int = 32
+    ffn: int = 16384
+    blocks: int = 28
+    head_dim: int = 128
+    qk_norm: bool = True
+    seed: int = 0
+
+    def __post_init__(self):
+        if self.heads * self.head_dim != self.hidden or self.head_dim != 128:
+            raise ValueError('hidden must equal heads * 128')
+        if self.hidden % 128 or self.ffn % 128:
+            raise ValueError('hidden and ffn must be multiples of 128')
+
+
+NANO = DiTConfig(4096, 32, 16384, 28)      # Cosmos3-Nano-shaped step (BASELINE config 3)
+SUPER = DiTConfig(6144, 48, 24576, 48)     # Cosmos3-Super-shaped step (BASELINE config 4)
+
+
+class _Source:
+    """Minimal stand-in for nn.Linear handed to RepairLinear."""
+
+    def __init__(self, weight):
+        self.weight, self.bias = weight, None
+        self.out_features, self.in_features = weight.shape
+
+
+def rms_norm(x, eps=1e-6):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)).to(x.dtype)
+
+
+class DiTBlock(torch.nn.Module):
+    def __init__(self, cfg, index, controller, topo, device):
+        super().__init__()
+        self.cfg, self.index, self.controller, self.topo = cfg, index, controller, topo
+        tp, r = topo.tp_size, topo.tp_rank
+        gen = torch.Generator(device='cpu').manual_seed(cfg.seed * 100003 + index)
+        make = lambda n, k: (torch.randn(n, k, generator=gen) * 0.02).bfloat16().to(device)
+        h, f = cfg.hidden, cfg.ffn
+        nb_h, kb_h, nb_f = h // 128, h // 128, f // 128
+        self.local_heads = cfg.heads // tp
+        full = {'qkv': make(3 * h, h), 'out': make(h, h), 'up': make(f, h), 'down': make(h, f)}
+        shards = {'qkv': parallel.shard_qkv(full['qkv'], cfg.heads, tp, r), 'out': parallel.shard_rows(full['out'], tp, r),
+                  'up': parallel.shard_columns(full['up'], tp, r), 'down': parallel.shard_rows(full['down'], tp, r)}
+        lattice = {'qkv': (3 * nb_h, kb_h, 'qkv'), 'out': (nb_h, kb_h, 'row'), 'up': (nb_f, kb_h, 'column'),
+                   'down': (nb_h, nb_f, 'row')}
+        self.split = {}
+        for part, w in shards.items():
+            name = f'blocks.{index}.{part}'
+            nb, kb, split = lattice[part]
+            tile_map = self._tile_map(nb, kb, split, tp, r, cfg.heads)
+            controller.register_linear(name, split, tile_map, tp)
+            self.split[part] = split
+            setattr(self, part, RepairLinear(_Source(w.contiguous()), controller, name, LinearSpec(), tile_map=tile_map))
+        del full, shards
+
+    @staticmethod
+    def _tile_map(nb, kb, split, tp, r, heads):
+        if tp == 1:
+            return None
+        if split == 'qkv':          # N blocks = [q heads | k heads | v heads], one block per head
+            per = heads // tp
+
+            def qkv_map(ids):
+                out = []
+                for t in ids:
+                    b, k = divmod(t, kb)
+                    which, head = divmod(b, heads)
+                    if r * per <= head < (r + 1) * per:
+                        out.append((which * per + head - r * per) * kb + k)
+                return sorted(out)
+            return qkv_map
+        return lambda ids: parallel.remap_tiles(ids, nb, kb, tp, r, split)
+
+    def _row_split(self, layer, x):
+        """Row-split linear: global activation factor, local GEMM, summed partial outputs."""
+        if self.topo.tp_size == 1:
+            return layer(x)
+        factor = parallel.global_factor(x, self.topo)
+        return parallel.allreduce_sum(layer(x, factor=factor), self.topo)
+
+    def forward(self, x, mod):
+        b, s, h = x.shape
+        shift1, scale1, gate1, shift2, scale2, gate2 = mod.unbind(1)
+        y = rms_norm(x) * (1 + scale1[:, None]) + shift1[:, None]
+        qkv = self.qkv(y).reshape(b, s, 3, self.local_heads, 128)
+        q, k, v = qkv.unbind(2)
+        if self.cfg.qk_norm:
+            q, k = rms_norm(q), rms_norm(k)
+        a = self.controller.attend(self.index, q, k, v).reshape(b, s, self.local_heads * 128)
+        x = x + gate1[:, None] * self._row_split(self.out, a)
+        y = rms_norm(x) * (1 + scale2[:, None]) + shift2[:, None]
+        u = torch.nn.functional.gelu(self.up(y), approximate='tanh')
+        return x + gate2[:, None] * self._row_split(self.down, u)
+
+
+class DiTModel(torch.nn.Module):
+    def __init__(self, cfg, controller, topo=None, device='cuda'):
+        super().__init__()
+        self.cfg = cfg
+        self.topo = topo or parallel.Topology()
+        self.blocks = torch.nn.ModuleList(DiTBlock(cfg, i, controller, self.topo, device) for i in range(cfg.blocks))
+
+    def forward(self, x, mod):
+        """x bf16 [batch, tokens, hidden]; mod bf16 [batch, blocks, 6, hidden] (AdaLN shift/scale/gate)."""
+        for i, block in enumerate(self.blocks):
+            x = block(x, mod[:, i])
+        return rms_norm(x)

@@ -18,8 +18,10 @@ from .assets import compact, expand
 
 
 class RepairLinear(torch.nn.Module):
-    def __init__(self, source, controller, name, spec, asset=None):
+    def __init__(self, source, controller, name, spec, asset=None, tile_map=None):
         super().__init__()
+        # tile_map: plan tile ids of the full layer -> ids of this (tensor-parallel) shard's lattice
+        self.tile_map = tile_map
         self.in_features, self.out_features = source.in_features, source.out_features
         self.controller, self.name, self.default = controller, name, spec
         self.repair_energy = getattr(getattr(controller, 'config', None), 'activation_repair_energy', 1.)
@@ -33,7 +35,7 @@ class RepairLinear(torch.nn.Module):
             # residual magnitude per tile: deterministic offline fallback score for W1 selection
             score = scales[1].float().reshape(n // 128, 128, k // 128, 8).square().sum((1, 3))
             asset = dict(codes=codes.cpu(), scales=scales.cpu(), factor=factor.cpu(), prescale=torch.ones(k),
-                         score=score.cpu(), bias=None if source.bias is None else source.bias.detach().cpu())
+                         identity_prescale=True, score=score.cpu(), bias=None if source.bias is None else source.bias.detach().cpu())
             if plan is not None:
                 asset.update(selector='residual_sensitivity', activation_sensitivity=w.float().square().sum(0).cpu())
         # with a plan only the union of W1 tiles any phase/branch selects is kept
@@ -48,8 +50,11 @@ class RepairLinear(torch.nn.Module):
         self.ops, self.bound, self.weight_bank = {}, None, None
 
     def _plan_union(self, plan):
-        return sorted(set(i for key, row in plan.linears.items() if key.split('|', 2)[-1] == self.name
-                          for i in row['w_blocks']))
+        ids = set()
+        for key, row in plan.linears.items():
+            if key.split('|', 2)[-1] == self.name:
+                ids.update(self.tile_map(row['w_blocks']) if self.tile_map else row['w_blocks'])
+        return sorted(ids)
 
     def export(self):
         return expand(self.asset, self.weight_union) if self.weight_union is not None else self.asset
