@@ -1,0 +1,60 @@
+"""Tensor-parallel DiT step on two GPUs (NCCL): TP2 output against the single-GPU output of the same
+seeded model. With full (or no) A repair the sharded quantizer produces the same bytes as the
+unsharded one (global factor); what differs is that each rank rounds its partial sum of a row-split
+layer to bf16 before the all-reduce (two roundings of larger partials instead of one of the total).
+Bound: relative L2 <= 4e-3 after two blocks. Needs two GPUs; skipped otherwise."""
+import os
+import socket
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(rank, world, port, results):
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), NCCL_NVLS_ENABLE='0')
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
+    try:
+        from thunderworld_b200 import parallel
+        from thunderworld_b200.cosmos.dit import DiTConfig, DiTModel
+        from thunderworld_b200.cosmos.engine import StepEngine
+        from thunderworld_b200.cosmos.settings import LinearSpec, RunConfig
+        from thunderworld_b200.config import RepairConfig, RepairPolicy
+        cfg = DiTConfig(hidden=512, heads=4, ffn=1024, blocks=2, seed=3)
+        run = RunConfig(execution='graph', ffn=LinearSpec(1., 1.), projection=LinearSpec(1., 1.),
+                        attention=RepairPolicy(RepairConfig(coverage=1., terms=3)), tensor_parallel=world)
+        g = torch.Generator().manual_seed(0)
+        x = torch.randn(2, 300, cfg.hidden, generator=g).bfloat16().cuda()
+        mod = (torch.randn(2, cfg.blocks, 6, cfg.hidden, generator=g) * 0.1).bfloat16().cuda()
+        outs = {}
+        for name, topo in (('tp', parallel.make_topology(tp_size=world)), ('single', parallel.Topology())):
+            engine = StepEngine(run, topo=topo)
+            model = DiTModel(cfg, engine, topo)
+            engine.warm_schedule(model, x=x, mod=mod)
+            a = engine(model, x=x, mod=mod)
+            b = engine(model, x=x, mod=mod)               # replay of the captured graph (incl. NCCL)
+            assert torch.equal(a, b)
+            outs[name] = a.float()
+            assert engine.device_status() == 0
+        rel = float((outs['tp'] - outs['single']).norm() / outs['single'].norm())
+        results[rank] = rel
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
+def test_tp2_matches_single_gpu():
+    ctx = mp.get_context('spawn')
+    results = ctx.Manager().dict()
+    with socket.socket() as s:
+        s.bind(('127.0.0.1', 0)); port = s.getsockname()[1]
+    procs = [ctx.Process(target=_run, args=(r, 2, port, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(600)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert all(rel <= 4e-3 for rel in results.values()), dict(results)
