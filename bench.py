@@ -179,6 +179,99 @@ def workload_config(budget, world, m=M_TOKENS, layers='qkv,out,ffn_up,ffn_down')
             'l2': 'per-step working set ~0.55 GB (activations, packed planes, outputs) exceeds the 126 MB L2'}
 
 
+def step_plan(cfg, budget, seed=0):
+    """Seeded issued-work plan of a DiT: per layer a = KB/2 (KB/4 at 1.5x) and 50 % (25 %) of the W1 tiles,
+    the same for both CFG branches and all four phases; attention quotas cover the same fraction of key tiles."""
+    from thunderworld_b200.cosmos.budget import RepairPlan
+    h, f = cfg.hidden // 128, cfg.ffn // 128
+    lattice = {'qkv': (3 * h, h), 'out': (h, h), 'up': (f, h), 'down': (h, f)}
+    frac = 0. if budget <= 1. else (0.25 if budget < 1.75 else 0.5)
+    rng = np.random.default_rng(seed)
+    linears, attention = {}, {}
+    for i in range(cfg.blocks):
+        for part, (nb, kb) in lattice.items():
+            tiles = sorted(int(t) for t in rng.permutation(nb * kb)[:int(frac * nb * kb)])
+            row = {'a_blocks': int(frac * kb), 'w_blocks': tiles, 'cross': False}
+            for b in range(2):
+                for ph in range(4):
+                    linears[f'{b}|{ph}|blocks.{i}.{part}'] = row
+    return RepairPlan(dict(schema_version=1, budget=max(budget, 1.), steps=35, phases=[0, 7, 18, 28, 35], task='t2v',
+                           linears=linears, attention={})), frac
+
+
+def run_step(args):
+    """DiT denoise-step time (BASELINE configs 3 and 4): one graph replay of the whole step, CFG batch 2
+    (split over GPU pairs when --cfg-parallel 2), tensor parallel over the remaining ranks."""
+    import torch
+    import torch.distributed as dist
+    from thunderworld_b200 import parallel
+    from thunderworld_b200.config import RepairConfig, RepairPolicy
+    from thunderworld_b200.cosmos import dit
+    from thunderworld_b200.cosmos.engine import StepEngine
+    from thunderworld_b200.cosmos.settings import RunConfig
+    rank, world = int(os.environ.get('RANK', '0')), int(os.environ.get('WORLD_SIZE', '1'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    torch.cuda.set_device(local)
+    device = torch.device('cuda', local)
+    if world > 1:
+        os.environ.setdefault('NCCL_NVLS_ENABLE', '0')
+        dist.init_process_group('nccl', device_id=device)
+    cfg_par = args.cfg_parallel
+    topo = parallel.make_topology(tp_size=world // cfg_par, cfg_size=cfg_par) if world > 1 else parallel.Topology()
+    base = {'nano': dit.NANO, 'super': dit.SUPER}[args.model]
+    cfg = dit.DiTConfig(base.hidden, base.heads, base.ffn, args.blocks or base.blocks)
+    plan, frac = step_plan(cfg, args.budget)
+    nt = (args.tokens + 127) // 128
+    quota = max(0, int(nt * frac) - 1)          # one tile less than the fraction: leaves room for the selector's own MMAs
+    local_heads = cfg.heads // topo.tp_size
+    run = RunConfig(compute_budget=max(args.budget, 1.),
+                    attention=RepairPolicy(RepairConfig(coverage=0., head_quotas=(quota,) * local_heads, terms=3)))
+    engine = StepEngine(run, plan=plan, topo=topo, branches=1)
+    engine._branch_offset = topo.cfg_rank if cfg_par > 1 else 0
+    model = dit.DiTModel(cfg, engine, topo, device)
+    batch = 2 // cfg_par
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(batch, args.tokens, cfg.hidden, generator=g)
+    cols = torch.randperm(cfg.hidden, generator=g)[:max(1, round(0.005 * cfg.hidden))]
+    x[..., cols] *= 20
+    x = x.bfloat16().to(device)
+    mod = (torch.randn(batch, cfg.blocks, 6, cfg.hidden, generator=g) * 0.1).bfloat16().to(device)
+    engine.warm_schedule(model, x=x, mod=mod)
+    ledger = engine.compile_budget() if args.budget > 1. else None
+    for _ in range(max(args.warmup, 3)):
+        engine.reset_request()
+        engine(model, x=x, mod=mod)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        engine.reset_request()
+        engine(model, x=x, mod=mod)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        rows = list(engine.rows.values())
+        # one (branch, phase) of the schedule = the work of one step; attention rows are per batch entry
+        issued = sum(r['total_mma'] * (batch if r['kind'] == 'attention' else 1) for r in rows
+                     if r['phase'] == 0 and r['branch'] == engine._branch_offset) * topo.tp_size * cfg_par
+        print(json.dumps({'metric': 'DiT denoise-step ms', 'value': float(t[0]), 'unit': 'ms', 'n_gpus': world,
+                          'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': float(t[0]),
+                          'higher_is_better': False, 'scaling': 'strong', 'vs_baseline': None,
+                          'dtype': 'nvfp4 (e2m1 x ue4m3, fp32 accumulate)', 'data': 'synthetic',
+                          'config': {'workload': f'{args.model}-shaped DiT step, {cfg.blocks} blocks, hidden {cfg.hidden}, '
+                                                 f'{args.tokens} tokens x CFG 2, {args.budget}x plan, CUDA Graph replay',
+                                     'parallelism': f'tp{topo.tp_size} x cfg{cfg_par}'},
+                          'issued_tflop_per_step': issued / 1e12, 'effective_tflops': issued / 1e12 / (float(t[0]) * 1e-3),
+                          'ledger_ratio': None if ledger is None else ledger['ratio']}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -190,7 +283,14 @@ def main():
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer timing (profiling runs)')
     ap.add_argument('--m-tokens', type=int, default=M_TOKENS, help='rows per projection (smaller for profiler captures)')
     ap.add_argument('--layers', default='qkv,out,ffn_up,ffn_down', help='subset of the projection set')
+    ap.add_argument('--workload', default='projections', choices=('projections', 'step'))
+    ap.add_argument('--model', default='nano', choices=('nano', 'super'))
+    ap.add_argument('--blocks', type=int, default=0, help='override the number of DiT blocks (step workload)')
+    ap.add_argument('--tokens', type=int, default=3840)
+    ap.add_argument('--cfg-parallel', type=int, default=1)
     args = ap.parse_args()
+    if args.workload == 'step':
+        return run_step(args)
     if args.impl == 'reference':
         return run_reference(args)
 
