@@ -272,6 +272,51 @@ def run_step(args):
         dist.destroy_process_group()
 
 
+def run_attention(args):
+    """Streaming FP4 attention (BASELINE config 2): batch 2 (CFG) x heads x seq x 128, self- and
+    cross-attention (512 text keys), base and 50 % / 3-term repair; time includes packing and selection."""
+    import torch
+    from thunderworld_b200 import RepairConfig
+    from thunderworld_b200.runtime import _forward
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(0)
+    B, H, S = 2, args.att_heads, args.tokens
+    results = {}
+    for name, sk in (('self', S), ('cross', 512)):
+        mk = lambda s_: (torch.randn(B, s_, H, 128, generator=g) * (torch.rand(H, generator=g) * 1.5 + .5)[None, None, :, None]).bfloat16().cuda()
+        q, k, v = mk(S), mk(sk), mk(sk)
+        for label, cfg in (('base', RepairConfig(coverage=0.)), ('repair50_terms3', RepairConfig(coverage=.5, terms=3))):
+            quotas = (torch.tensor(cfg.head_counts(H, sk), device='cuda', dtype=torch.int32),
+                      torch.tensor(cfg.pv_counts(H, sk), device='cuda', dtype=torch.int32))
+            for _ in range(3):
+                _forward(q, k, v, cfg, None, quotas)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                held = _forward(q, k, v, cfg, None, quotas)
+            for _ in range(max(args.warmup, 3)):
+                graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            nt = (sk + 127) // 128
+            issued = 4 * B * H * S * nt * 128 * 128 * (1 + (cfg.terms - 1) * sum(cfg.head_counts(H, sk)) / (H * nt))
+            results[f'{name}_{label}'] = {'ms': ms, 'issued_tflop': issued / 1e12, 'tflops': issued / 1e12 / (ms * 1e-3)}
+    best = results['self_base']
+    print(json.dumps({'metric': 'streaming FP4 attention effective TFLOPS on issued FP4 work', 'value': best['tflops'],
+                      'unit': 'TFLOP/s', 'n_gpus': 1, 'steps': args.steps, 'warmup': max(args.warmup, 3),
+                      'ms_per_step': best['ms'], 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+                      'dtype': 'nvfp4 (e2m1 x ue4m3, fp32 softmax)', 'data': 'synthetic',
+                      'config': {'workload': f'attention config 2: batch 2 x {H} heads x seq {S} x 128, cross 512 keys'},
+                      'cases': results,
+                      'roofline': {'bound': 'tensor', 'achieved': best['tflops'], 'peak': NOMINAL_FP4_TFLOPS, 'unit': 'TFLOP/s',
+                                   'frac': best['tflops'] / NOMINAL_FP4_TFLOPS, 'traffic': None}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -283,14 +328,17 @@ def main():
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer timing (profiling runs)')
     ap.add_argument('--m-tokens', type=int, default=M_TOKENS, help='rows per projection (smaller for profiler captures)')
     ap.add_argument('--layers', default='qkv,out,ffn_up,ffn_down', help='subset of the projection set')
-    ap.add_argument('--workload', default='projections', choices=('projections', 'step'))
+    ap.add_argument('--workload', default='projections', choices=('projections', 'step', 'attention'))
     ap.add_argument('--model', default='nano', choices=('nano', 'super'))
     ap.add_argument('--blocks', type=int, default=0, help='override the number of DiT blocks (step workload)')
     ap.add_argument('--tokens', type=int, default=3840)
     ap.add_argument('--cfg-parallel', type=int, default=1)
+    ap.add_argument('--att-heads', type=int, default=32)
     args = ap.parse_args()
     if args.workload == 'step':
         return run_step(args)
+    if args.workload == 'attention':
+        return run_attention(args)
     if args.impl == 'reference':
         return run_reference(args)
 
