@@ -92,10 +92,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: polls until the phase with `parity` completes, the CTA-wide
-// abort flag is raised, or about `limit_cycles` SM cycles have passed. On a
+// abort flag is raised, or about `limit_cycles` SM cycles (about half a second) have passed. On a
 // timeout it raises the abort flag and returns false; it never traps.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          long long limit_cycles = 4000000000LL) {
+                                          long long limit_cycles = 1000000000LL) {
   if (mbar_try_wait(bar, parity)) return true;
   long long start = clock64();
   uint32_t polls = 0;
@@ -112,7 +112,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // short sleep between polls, so that idle warps do not take issue slots from the single-thread
 // producer and MMA roles; the other lanes block at the warp barrier.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                               long long limit_cycles = 4000000000LL) {
+                                               long long limit_cycles = 1000000000LL) {
   int ok = 1;
   if ((threadIdx.x & 31) == 0) {
     if (!mbar_try_wait(bar, parity)) {

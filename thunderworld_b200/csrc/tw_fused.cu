@@ -57,13 +57,13 @@ template <int BN> struct Cfg {
   static constexpr int OFF_TAB = OFF_SFW1 + W1_SLOTS * SF_ATOM;
   static constexpr int TAB_BYTES = HALVES * KB_MAX * 4 + (HALVES + 1) * (KB_MAX / 32) * 4;
   static constexpr int OFF_BAR = OFF_TAB + TAB_SLOTS * TAB_BYTES;
-  static constexpr int NUM_BARS = 2 * STAGES + 2 * A1_SLOTS + 2 * W1_SLOTS + 2 * TAB_SLOTS + 2 * ACC_STAGES + 4 + A1_SLOTS + W1_SLOTS;
+  static constexpr int NUM_BARS = 2 * STAGES + 2 * A1_SLOTS + 2 * W1_SLOTS + 2 * TAB_SLOTS + 2 * ACC_STAGES + STAGES + A1_SLOTS + W1_SLOTS;
   static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 64 + 1024;  // + alignment slack
   // tensor-memory columns: accumulators, then double-buffered scale regions
   static constexpr int TM_ACC = 0;
-  static constexpr int TM_SFA0 = ACC_STAGES * BN;                        // 2 x 16 columns
-  static constexpr int TM_SFB0 = TM_SFA0 + 32;                           // 2 x 16*HALVES columns
-  static constexpr int TM_SFA1 = TM_SFB0 + 32 * HALVES;                  // 8 columns per A1 slot
+  static constexpr int TM_SFA0 = ACC_STAGES * BN;                        // STAGES x 16 columns: one region per smem stage
+  static constexpr int TM_SFB0 = TM_SFA0 + 16 * STAGES;                  // STAGES x 16*HALVES columns
+  static constexpr int TM_SFA1 = TM_SFB0 + 16 * HALVES * STAGES;                  // 8 columns per A1 slot
   static constexpr int TM_SFW1 = TM_SFA1 + 32;                           // 8 columns per W1 slot
   static constexpr int TM_COLS = 512;
   static_assert(A1_SLOTS * 8 <= 32 && TM_SFW1 + 8 * W1_SLOTS <= TM_COLS, "tensor memory budget");
@@ -151,9 +151,8 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
   uint64_t* tabEmpty = tabFull + C::TAB_SLOTS;
   uint64_t* accFull = tabEmpty + C::TAB_SLOTS;
   uint64_t* accEmpty = accFull + C::ACC_STAGES;
-  uint64_t* sfFull = accEmpty + C::ACC_STAGES;   // base-stage scales resident in TMEM region [step parity]
-  uint64_t* sfEmpty = sfFull + 2;
-  uint64_t* usfA = sfEmpty + 2;                  // scales of the A1 unit in slot i are in TMEM
+  uint64_t* sfFull = accEmpty + C::ACC_STAGES;   // scales of the base stage in slot i are in its TMEM region
+  uint64_t* usfA = sfFull + C::STAGES;                  // scales of the A1 unit in slot i are in TMEM
   uint64_t* usfW = usfA + C::A1_SLOTS;           // same for W1 units
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(usfW + C::W1_SLOTS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -170,7 +169,7 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
     for (int i = 0; i < C::W1_SLOTS; ++i) { tw::mbar_init(fullW1 + i, 1); tw::mbar_init(emptyW1 + i, 1); }
     for (int i = 0; i < C::TAB_SLOTS; ++i) { tw::mbar_init(tabFull + i, 1); tw::mbar_init(tabEmpty + i, 2 + C::SF_THREADS); }
     for (int i = 0; i < C::ACC_STAGES; ++i) { tw::mbar_init(accFull + i, 1); tw::mbar_init(accEmpty + i, C::EPI_WARPS); }
-    for (int i = 0; i < 2; ++i) { tw::mbar_init(sfFull + i, C::SF_THREADS); tw::mbar_init(sfEmpty + i, 1); }
+    for (int i = 0; i < C::STAGES; ++i) tw::mbar_init(sfFull + i, C::SF_THREADS);
     for (int i = 0; i < C::A1_SLOTS; ++i) tw::mbar_init(usfA + i, 1);
     for (int i = 0; i < C::W1_SLOTS; ++i) tw::mbar_init(usfW + i, 1);
     *abort_flag = 0;
@@ -283,7 +282,6 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
       const uint32_t a1_base = (smem_u + C::OFF_A1) >> 4, w1_base = (smem_u + C::OFF_W1) >> 4;
       const uint32_t t_sfa0_b = tmem + C::TM_SFA0, t_sfb0_b = tmem + C::TM_SFB0;
       uint32_t s = 0, ph = 0;                  // base stage slot / phase
-      uint32_t sfp = 0, sfph = 0;              // TMEM scale region (step parity) / its barrier phase
       uint32_t sa = 0, pa = 0, sw = 0, pw = 0; // unit slots / phases
       uint32_t it = 0, tsl = 0, tph = 0;       // tile counter, table slot / phase
       for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
@@ -305,11 +303,11 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
             for (int h = 0; h < C::HALVES; ++h) wbits[h] = tab.w1bits[h][kb0 >> 5];
           }
           // the scale-copy threads waited for the stage's data and moved its scales into TMEM
-          ok = tw::mbar_wait(sfFull + sfp, sfph, abort_flag) && tw::mbar_wait(fullS + s, ph, abort_flag);
+          ok = tw::mbar_wait(sfFull + s, ph, abort_flag) && tw::mbar_wait(fullS + s, ph, abort_flag);
           if (!ok) break;
           tw::tc_fence_after();
           const uint32_t a0_lo = a0_base + s * (C::A0_TILE >> 4), w0_lo = w0_base + s * (C::W0_TILE >> 4);
-          const uint32_t t_sfa0 = t_sfa0_b + sfp * 16, t_sfb0 = t_sfb0_b + sfp * 16 * C::HALVES;
+          const uint32_t t_sfa0 = t_sfa0_b + s * 16, t_sfb0 = t_sfb0_b + s * 16 * C::HALVES;
 #pragma unroll
           for (int q = 0; q < 4; ++q)                              // A0 W0
             if (q < nq)
@@ -371,9 +369,7 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
             }
           }
           tw::tc_commit(emptyS + s);
-          tw::tc_commit(sfEmpty + sfp);
           if (++s == C::STAGES) { s = 0; ph ^= 1; }
-          if (++sfp == 2) { sfp = 0; sfph ^= 1; }
           abits >>= 2;
 #pragma unroll
           for (int h = 0; h < C::HALVES; ++h) wbits[h] >>= 2;
@@ -388,8 +384,8 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
     // Issuing a tcgen05.cp costs its thread tens of cycles and a K256 step needs 4 * (1 + BN/128)
     // of them plus two per repair unit, so they are issued by two threads of their own instead of
     // the MMA issuer: thread 0 takes K64 slices {0,1} of the base stage and the A1 units, thread 1
-    // slices {2,3} and the W1 units. Base-stage TMEM regions are double-buffered by step parity;
-    // a unit's region belongs to its smem slot and is free again whenever that slot was reloaded.
+    // slices {2,3} and the W1 units. Every smem stage / unit slot owns a TMEM scale region, which is
+    // free again whenever that stage or slot was reloaded (its previous MMAs had finished by then).
     if (lane == 0) {
       const int c = warp - 4;
       constexpr uint64_t DSF = (uint64_t(1) << 46) | (uint64_t(128 >> 4) << 32);
@@ -400,7 +396,7 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
       uint64_t* const unit_full = c == 0 ? fullA1 : fullW1;
       uint64_t* const unit_ready = c == 0 ? usfA : usfW;
       const uint32_t unit_slots = c == 0 ? C::A1_SLOTS : C::W1_SLOTS;
-      uint32_t s = 0, ph = 0, sfp = 0, sfph = 0, su = 0, pu = 0, it = 0;
+      uint32_t s = 0, ph = 0, su = 0, pu = 0, it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
         const int n_rows = min(BN, p.n - (tile % p.tiles_n) * BN);
@@ -416,10 +412,11 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
               for (int h = 0; h < C::HALVES; ++h) bits[h] = tab.w1bits[h][kb0 >> 5];
             }
           }
-          ok = tw::mbar_wait(fullS + s, ph, abort_flag) && tw::mbar_wait(sfEmpty + sfp, sfph ^ 1, abort_flag);
+          // the stage was reloaded only after the MMAs of its previous use finished, so its region is free
+          ok = tw::mbar_wait(fullS + s, ph, abort_flag);
           if (!ok) break;
           const uint32_t sf_lo = sf0_base + s * (C::STAGE_SF >> 4);
-          const uint32_t t_sfa0 = tmem + C::TM_SFA0 + sfp * 16, t_sfb0 = tmem + C::TM_SFB0 + sfp * 16 * C::HALVES;
+          const uint32_t t_sfa0 = tmem + C::TM_SFA0 + s * 16, t_sfb0 = tmem + C::TM_SFB0 + s * 16 * C::HALVES;
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
             const int q = 2 * c + i;
@@ -431,9 +428,8 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
                   tw::tc_copy_scales(t_sfb0 + 4 * C::HALVES * q + 4 * h, DSF | (sf_lo + (1 + h) * 128 + q * 32));
             }
           }
-          tw::tc_commit(sfFull + sfp);
+          tw::tc_commit(sfFull + s);
           if (++s == C::STAGES) { s = 0; ph ^= 1; }
-          if (++sfp == 2) { sfp = 0; sfph ^= 1; }
           // units of this step, in the order the MMA issuer consumes them
           int count = 0;
           if (c == 0) count = __popc(bits[0] & 3u);
