@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(128) select_kernel(SelectParams p) {
 //   T = P0 V0 [+ P1 V0 + P0 V1 + P1 V1]                                          tcgen05, fp32 in TMEM
 //   acc = acc * alpha + T * pf[m] * vf[d]
 // Warps: 0 producer (TMA + bulk copies), 1 MMA issuer (scale copies smem -> TMEM, MMAs, commits),
-// 4..7 softmax / accumulate (row = TMEM lane). No cluster, no multicast.
+// 4..11 softmax / accumulate (row = TMEM lane, two warps per lane quadrant). No cluster, no multicast.
 namespace {
 
 constexpr int ATT_TILE = 128 * 64;        // bytes of a 128 x 128 NVFP4 code tile
@@ -300,7 +300,8 @@ struct AttSmem {
   static constexpr int OFF_KF = OFF_SFP + 2 * 2 * ATT_SF;           // slots x 128 floats
   static constexpr int OFF_VF = OFF_KF + ATT_SLOTS * 512;
   static constexpr int OFF_SEL = OFF_VF + ATT_SLOTS * 512;          // per key tile: bit0 QK repair, bit1 PV repair
-  static constexpr int OFF_BAR = OFF_SEL + ATT_NT_MAX;
+  static constexpr int OFF_XCHG = OFF_SEL + ATT_NT_MAX;             // 2 x 2 x 128 floats: row statistics between halves
+  static constexpr int OFF_BAR = OFF_XCHG + 2 * 2 * 128 * 4;
   static constexpr int NUM_BARS = 1 + 4 * ATT_SLOTS + 2 + 2 + 2 + 2 + 2;
   static constexpr int BYTES = OFF_BAR + NUM_BARS * 8 + 64 + 1024;
 };
@@ -319,7 +320,7 @@ __device__ __forceinline__ float exp2_approx(float x) {
   return r;
 }
 
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(384, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const AttParams p) {
   using L = AttSmem;
@@ -350,13 +351,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (threadIdx.x == 0) {
     tw::mbar_init(qFull, 1);
     for (int i = 0; i < ATT_SLOTS; ++i) {
-      tw::mbar_init(kFull + i, 1); tw::mbar_init(kEmpty + i, 5);   // MMA commit + 4 softmax warps (kf)
-      tw::mbar_init(vFull + i, 1); tw::mbar_init(vEmpty + i, 5);
+      tw::mbar_init(kFull + i, 1); tw::mbar_init(kEmpty + i, 9);   // MMA commit + 8 softmax warps (kf)
+      tw::mbar_init(vFull + i, 1); tw::mbar_init(vEmpty + i, 9);
     }
     for (int i = 0; i < 2; ++i) {
-      tw::mbar_init(sFull + i, 1); tw::mbar_init(sEmpty + i, 4);
-      tw::mbar_init(pFull + i, 4); tw::mbar_init(pEmpty + i, 1);
-      tw::mbar_init(tFull + i, 1); tw::mbar_init(tEmpty + i, 4);
+      tw::mbar_init(sFull + i, 1); tw::mbar_init(sEmpty + i, 8);
+      tw::mbar_init(pFull + i, 8); tw::mbar_init(pEmpty + i, 1);
+      tw::mbar_init(tFull + i, 1); tw::mbar_init(tEmpty + i, 8);
     }
     *abort_flag = 0;
     tw::fence_barrier_init();
@@ -484,14 +485,18 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ softmax, P quantization, accumulate
-    const int quad = warp & 3, r = quad * 32 + lane;            // r = query row within the tile = TMEM lane
-    const int m = mb * 128 + r;
+    // Eight warps: two per TMEM lane quadrant. A thread owns one query row and one half of the
+    // 128 columns (keys for S and P, channels for T and the accumulator); the two halves of a row
+    // exchange their partial row maximum through shared memory once per key tile.
+    const int quad = warp & 3, half = (warp - 4) >> 2, r = quad * 32 + lane;
+    const int m = mb * 128 + r, c0 = half * 64;
     const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
     const float qscale = (m < p.mp ? __ldg(p.qf + (size_t)h * p.mp + m) : 1.f) * 0.08838834764831845f;
     constexpr float LOG2E = 1.4426950408889634f;
-    float acc[128];
+    float* xchg = reinterpret_cast<float*>(smem + L::OFF_XCHG);       // [2][2][128]: parity, half, row
+    float acc[64];
 #pragma unroll
-    for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+    for (int i = 0; i < 64; ++i) acc[i] = 0.f;
     float mx = -INFINITY, den = 0.f;
     bool ok = true;
     for (int t = 0; t < p.nt && ok; ++t) {
@@ -501,14 +506,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tw::tc_fence_after();
-      const float* kf = reinterpret_cast<const float*>(smem + L::OFF_KF + s * 512);
-      const int n_valid = p.n - t * 128;                      // columns >= n_valid are padding
-      // pass 1: row maximum of the scaled scores
+      const float* kf = reinterpret_cast<const float*>(smem + L::OFF_KF + s * 512) + c0;
+      const int n_valid = p.n - t * 128 - c0;                 // columns >= n_valid of this half are padding
+      // pass 1: row maximum of the scaled scores (this half), then the other half's through smem
       float rowmax = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
-        tw::tmem_load_32x32(lane_base + TM_S + par * 128 + c * 32, v);
+        tw::tmem_load_32x32(lane_base + TM_S + par * 128 + c0 + c * 32, v);
         tw::tmem_load_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -516,6 +521,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           rowmax = fmaxf(rowmax, (c * 32 + i) < n_valid ? sc : -INFINITY);
         }
       }
+      xchg[(par * 2 + half) * 128 + r] = rowmax;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      rowmax = fmaxf(rowmax, xchg[(par * 2 + (half ^ 1)) * 128 + r]);
       const float nm = fmaxf(mx, rowmax);
       const float alpha = exp2_approx((mx - nm) * LOG2E);
       const float pmax = exp2_approx((rowmax - nm) * LOG2E);
@@ -529,9 +537,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       float rowsum = 0.f;
       // pass 2: probabilities, their NVFP4 codes and scales, 32 columns at a time
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
-        tw::tmem_load_32x32(lane_base + TM_S + par * 128 + c * 32, v);
+        tw::tmem_load_32x32(lane_base + TM_S + par * 128 + c0 + c * 32, v);
         tw::tmem_load_wait();
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
@@ -546,7 +554,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             z[i] = pr * inv_pf;
             peak = fmaxf(peak, z[i]);
           }
-          const int grp = c * 2 + g;                                     // K16 group 0..7 of this row
+          const int grp = half * 4 + c * 2 + g;                          // K16 group 0..7 of this row
           const uint32_t sb = tw::f32_to_e4m3(fmaxf(peak * (1.f / 6.f), 0.001953125f));
           const float sv = tw::e4m3_to_f32(sb), inv_s = rcp_approx(sv);
           uint32_t w[2] = {0u, 0u};
@@ -575,23 +583,23 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           }
         }
       }
-      den = den * alpha + rowsum;
+      den = den * alpha + rowsum;                             // this half's share of the denominator
       mx = nm;
       // scores consumed, kf consumed, P visible to the tensor core (async proxy)
       tw::tc_fence_before();
       tw::fence_proxy_async();
       __syncwarp();
       if (lane == 0) { tw::mbar_arrive(sEmpty + par); tw::mbar_arrive(kEmpty + s); tw::mbar_arrive(pFull + par); }
-      // T = P V of this tile
+      // T = P V of this tile: this thread accumulates channels c0 .. c0 + 63 of its row
       ok = tw::mbar_wait(tFull, t & 1, abort_flag) && tw::mbar_wait(vFull + s, ph, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tw::tc_fence_after();
-      const float* vf = reinterpret_cast<const float*>(smem + L::OFF_VF + s * 512);
+      const float* vf = reinterpret_cast<const float*>(smem + L::OFF_VF + s * 512) + c0;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
-        tw::tmem_load_32x32(lane_base + TM_T + c * 32, v);
+        tw::tmem_load_32x32(lane_base + TM_T + c0 + c * 32, v);
         tw::tmem_load_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i)
@@ -601,11 +609,15 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       __syncwarp();
       if (lane == 0) { tw::mbar_arrive(tEmpty); tw::mbar_arrive(vEmpty + s); }
     }
+    // the two halves of a row add their denominators
+    xchg[half * 128 + r] = den;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    den += xchg[(half ^ 1) * 128 + r];
     if (ok && m < p.m) {
       const float inv = 1.f / den;
-      __nv_bfloat16* dst = p.out + ((size_t)m * p.hq + h) * 128;
+      __nv_bfloat16* dst = p.out + ((size_t)m * p.hq + h) * 128 + c0;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 4; ++j) {
         uint32_t w[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
@@ -729,6 +741,6 @@ extern "C" int tw_attention(const TwAttentionArgs* a, void* stream_) {
       return TW_ERR_LAUNCH;
     configured = true;
   }
-  attention_kernel<<<dim3((a->m + 127) / 128, a->hq), 256, AttSmem::BYTES, static_cast<cudaStream_t>(stream_)>>>(tm_q, tm_k, tm_v, p);
+  attention_kernel<<<dim3((a->m + 127) / 128, a->hq), 384, AttSmem::BYTES, static_cast<cudaStream_t>(stream_)>>>(tm_q, tm_k, tm_v, p);
   return cudaGetLastError() == cudaSuccess ? TW_OK : TW_ERR_LAUNCH;
 }
