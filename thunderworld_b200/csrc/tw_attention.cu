@@ -4,6 +4,7 @@
 //   pack_qk :12-25, pack_v :29-47, streaming_attention :51-124, select_tiles_head :191-215
 // and the per-row-factor quantizer _quantize.py:7-39 (factor = max(|row|max / 1536, 1e-12)).
 // Packing is redone for every call; nothing about old inputs is cached. P is quantized on chip.
+#include <type_traits>
 #include <cuda.h>
 #include "tw_common.cuh"
 #include "../../include/twb200.h"
@@ -275,7 +276,7 @@ namespace {
 
 constexpr int ATT_TILE = 128 * 64;        // bytes of a 128 x 128 NVFP4 code tile
 constexpr int ATT_SF = 1024;
-constexpr int ATT_SLOTS = 2;
+constexpr int ATT_SLOTS = 3;
 constexpr int ATT_NT_MAX = 1024;
 
 struct AttParams {
@@ -300,8 +301,8 @@ struct AttSmem {
   static constexpr int OFF_KF = OFF_SFP + 2 * 2 * ATT_SF;           // slots x 128 floats
   static constexpr int OFF_VF = OFF_KF + ATT_SLOTS * 512;
   static constexpr int OFF_SEL = OFF_VF + ATT_SLOTS * 512;          // per key tile: bit0 QK repair, bit1 PV repair
-  static constexpr int OFF_XCHG = OFF_SEL + ATT_NT_MAX;             // 2 x 2 x 128 floats: row statistics between halves
-  static constexpr int OFF_BAR = OFF_XCHG + 2 * 2 * 128 * 4;
+  static constexpr int OFF_XCHG = OFF_SEL + ATT_NT_MAX;             // 3 x 2 x 128 floats: row maxima (two parities), denominators
+  static constexpr int OFF_BAR = OFF_XCHG + 3 * 2 * 128 * 4;
   static constexpr int NUM_BARS = 1 + 4 * ATT_SLOTS + 2 + 2 + 2 + 2 + 2;
   static constexpr int BYTES = OFF_BAR + NUM_BARS * 8 + 64 + 1024;
 };
@@ -488,27 +489,64 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // Eight warps: two per TMEM lane quadrant. A thread owns one query row and one half of the
     // 128 columns (keys for S and P, channels for T and the accumulator); the two halves of a row
     // exchange their partial row maximum through shared memory once per key tile.
+    // Everything runs in the log2 domain: x = S * kf[n] * (qf[m] * log2(e) / sqrt(128)). The scaled
+    // probability z = p / pf is produced directly as exp2(x - off) with off = nm + log2(pf), and
+    // pf = max(exp2(rowmax - nm) / 1536, 1e-12) is  exp2(off - nm)  with
+    // off = max(rowmax - log2(1536), nm + log2(1e-12)).
+    // The accumulation of P V of tile t is deferred until the scores of tile t + 1 have been reduced,
+    // so the P V product runs under the next tile's softmax instead of stalling these warps.
     const int quad = warp & 3, half = (warp - 4) >> 2, r = quad * 32 + lane;
     const int m = mb * 128 + r, c0 = half * 64;
     const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
-    const float qscale = (m < p.mp ? __ldg(p.qf + (size_t)h * p.mp + m) : 1.f) * 0.08838834764831845f;
-    constexpr float LOG2E = 1.4426950408889634f;
-    float* xchg = reinterpret_cast<float*>(smem + L::OFF_XCHG);       // [2][2][128]: parity, half, row
+    const float qfl = (m < p.mp ? __ldg(p.qf + (size_t)h * p.mp + m) : 1.f) * (0.08838834764831845f * 1.4426950408889634f);
+    float* xchg = reinterpret_cast<float*>(smem + L::OFF_XCHG);       // [3][2][128]: row maxima by tile parity, then denominators; half, row
     float acc[64];
 #pragma unroll
     for (int i = 0; i < 64; ++i) acc[i] = 0.f;
-    float mx = -INFINITY, den = 0.f;
+    float mx = -INFINITY, den = 0.f;                                   // running maximum (log2 domain), denominator share
+    float alpha_prev = 1.f, pf_prev = 0.f;
     bool ok = true;
-    for (int t = 0; t < p.nt && ok; ++t) {
+
+    // acc = acc * alpha + T * pf * vf for key tile u (channels c0 .. c0 + 63 of this row)
+    auto accumulate = [&](int u, float alpha, float pf) {
+      const uint32_t s = u % ATT_SLOTS, ph = (u / ATT_SLOTS) & 1;
+      bool good = tw::mbar_wait(tFull, u & 1, abort_flag) && tw::mbar_wait(vFull + s, ph, abort_flag);
+      good = __all_sync(0xffffffffu, good);
+      if (!good) return false;
+      tw::tc_fence_after();
+      const float4* vf = reinterpret_cast<const float4*>(smem + L::OFF_VF + s * 512) + (c0 >> 2);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t v[32];
+        tw::tmem_load_32x32(lane_base + TM_T + c0 + c * 32, v);
+        tw::tmem_load_wait();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 f = vf[c * 8 + i];
+          acc[c * 32 + 4 * i + 0] = __fmaf_rn(acc[c * 32 + 4 * i + 0], alpha, __uint_as_float(v[4 * i + 0]) * (pf * f.x));
+          acc[c * 32 + 4 * i + 1] = __fmaf_rn(acc[c * 32 + 4 * i + 1], alpha, __uint_as_float(v[4 * i + 1]) * (pf * f.y));
+          acc[c * 32 + 4 * i + 2] = __fmaf_rn(acc[c * 32 + 4 * i + 2], alpha, __uint_as_float(v[4 * i + 2]) * (pf * f.z));
+          acc[c * 32 + 4 * i + 3] = __fmaf_rn(acc[c * 32 + 4 * i + 3], alpha, __uint_as_float(v[4 * i + 3]) * (pf * f.w));
+        }
+      }
+      tw::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { tw::mbar_arrive(tEmpty); tw::mbar_arrive(vEmpty + s); }
+      return true;
+    };
+
+    // one key tile; TAIL: the tile holds padding columns (only the last tile of a ragged key length)
+    auto tile = [&](int t, auto tail_tag) {
+      constexpr bool TAIL = decltype(tail_tag)::value;
       const uint32_t s = t % ATT_SLOTS, ph = (t / ATT_SLOTS) & 1, par = t & 1;
       const bool rep = sel[t] & 2;
-      ok = tw::mbar_wait(sFull + par, (t >> 1) & 1, abort_flag) && tw::mbar_wait(kFull + s, ph, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      bool good = tw::mbar_wait(sFull + par, (t >> 1) & 1, abort_flag) && tw::mbar_wait(kFull + s, ph, abort_flag);
+      good = __all_sync(0xffffffffu, good);
+      if (!good) return false;
       tw::tc_fence_after();
-      const float* kf = reinterpret_cast<const float*>(smem + L::OFF_KF + s * 512) + c0;
+      const float4* kf = reinterpret_cast<const float4*>(smem + L::OFF_KF + s * 512) + (c0 >> 2);
       const int n_valid = p.n - t * 128 - c0;                 // columns >= n_valid of this half are padding
-      // pass 1: row maximum of the scaled scores (this half), then the other half's through smem
+      // pass 1: row maximum of S * kf over this half, the other half's through shared memory
       float rowmax = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -516,103 +554,110 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         tw::tmem_load_32x32(lane_base + TM_S + par * 128 + c0 + c * 32, v);
         tw::tmem_load_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float sc = __uint_as_float(v[i]) * qscale * kf[c * 32 + i];
-          rowmax = fmaxf(rowmax, (c * 32 + i) < n_valid ? sc : -INFINITY);
+        for (int i = 0; i < 8; ++i) {
+          const float4 f = kf[c * 8 + i];
+          const float e[4] = {__uint_as_float(v[4 * i]) * f.x, __uint_as_float(v[4 * i + 1]) * f.y,
+                              __uint_as_float(v[4 * i + 2]) * f.z, __uint_as_float(v[4 * i + 3]) * f.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            rowmax = fmaxf(rowmax, (!TAIL || (c * 32 + 4 * i + j) < n_valid) ? e[j] : -INFINITY);
         }
       }
+      rowmax *= qfl;                                          // qfl > 0
       xchg[(par * 2 + half) * 128 + r] = rowmax;
       asm volatile("bar.sync 1, 256;" ::: "memory");
       rowmax = fmaxf(rowmax, xchg[(par * 2 + (half ^ 1)) * 128 + r]);
       const float nm = fmaxf(mx, rowmax);
-      const float alpha = exp2_approx((mx - nm) * LOG2E);
-      const float pmax = exp2_approx((rowmax - nm) * LOG2E);
-      const float pf = fmaxf(pmax * (1.f / 1536.f), 1.0e-12f), inv_pf = rcp_approx(pf);
+      const float alpha = exp2_approx(mx - nm);
+      const float off = fmaxf(rowmax - 10.584962500721156f, nm - 39.863137138648348f);
+      const float pf = exp2_approx(off - nm);
+      // deferred accumulation of the previous tile: its P V product had this tile's first pass to finish
+      if (t > 0 && !accumulate(t - 1, alpha_prev, pf_prev)) return false;
+      alpha_prev = alpha; pf_prev = pf;
       // the P buffer of this parity must have been consumed by the PV product two tiles ago
-      ok = tw::mbar_wait(pEmpty + par, ((t >> 1) & 1) ^ 1, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      good = tw::mbar_wait(pEmpty + par, ((t >> 1) & 1) ^ 1, abort_flag);
+      good = __all_sync(0xffffffffu, good);
+      if (!good) return false;
       uint8_t* p0 = smem + L::OFF_P + par * 2 * ATT_TILE;
       uint8_t* sfp = smem + L::OFF_SFP + par * 2 * ATT_SF;
-      float rowsum = 0.f;
-      // pass 2: probabilities, their NVFP4 codes and scales, 32 columns at a time
+      float zsum = 0.f;
+      uint32_t sf_base = 0u, sf_res = 0u;
+      // pass 2: scaled probabilities, their NVFP4 codes and scales, 32 columns at a time
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
         tw::tmem_load_32x32(lane_base + TM_S + par * 128 + c0 + c * 32, v);
         tw::tmem_load_wait();
+        uint32_t w[4], rw[4];
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
           float z[16];
           float peak = 0.f;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int col = c * 32 + g * 16 + i;
-            const float sc = __uint_as_float(v[g * 16 + i]) * qscale * kf[col];
-            const float pr = col < n_valid ? exp2_approx((sc - nm) * LOG2E) : 0.f;
-            rowsum += pr;
-            z[i] = pr * inv_pf;
-            peak = fmaxf(peak, z[i]);
+          for (int i = 0; i < 4; ++i) {
+            const float4 f = kf[c * 8 + g * 4 + i];
+            const float e[4] = {__uint_as_float(v[g * 16 + 4 * i]) * f.x, __uint_as_float(v[g * 16 + 4 * i + 1]) * f.y,
+                                __uint_as_float(v[g * 16 + 4 * i + 2]) * f.z, __uint_as_float(v[g * 16 + 4 * i + 3]) * f.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float zz = exp2_approx(__fmaf_rn(e[j], qfl, -off));
+              if (TAIL && (c * 32 + g * 16 + 4 * i + j) >= n_valid) zz = 0.f;
+              z[4 * i + j] = zz;
+              zsum += zz;
+              peak = fmaxf(peak, zz);
+            }
           }
-          const int grp = half * 4 + c * 2 + g;                          // K16 group 0..7 of this row
           const uint32_t sb = tw::f32_to_e4m3(fmaxf(peak * (1.f / 6.f), 0.001953125f));
           const float sv = tw::e4m3_to_f32(sb), inv_s = rcp_approx(sv);
-          uint32_t w[2] = {0u, 0u};
+          w[2 * g] = w[2 * g + 1] = 0u;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) w[i >> 2] |= tw::f32x2_to_e2m1x2(z[2 * i] * inv_s, z[2 * i + 1] * inv_s) << (8 * (i & 3));
-          const uint32_t code_off = (uint32_t)r * 64u + (uint32_t)(((grp >> 1) ^ ((r >> 1) & 3)) << 4) + (uint32_t)(grp & 1) * 8u;
-          *reinterpret_cast<uint2*>(p0 + code_off) = make_uint2(w[0], w[1]);
-          sfp[atom_offset(r, grp)] = (uint8_t)sb;
+          for (int i = 0; i < 8; ++i) w[2 * g + (i >> 2)] |= tw::f32x2_to_e2m1x2(z[2 * i] * inv_s, z[2 * i + 1] * inv_s) << (8 * (i & 3));
+          sf_base |= sb << (8 * (c * 2 + g));
           if (rep) {
             float res[16];
             float rpeak = 0.f;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const float2 val = e2m1x2_values((w[i >> 2] >> (8 * (i & 3))) & 0xffu);
+              const float2 val = e2m1x2_values((w[2 * g + (i >> 2)] >> (8 * (i & 3))) & 0xffu);
               res[2 * i] = __fmaf_rn(-val.x, sv, z[2 * i]);
               res[2 * i + 1] = __fmaf_rn(-val.y, sv, z[2 * i + 1]);
               rpeak = fmaxf(rpeak, fmaxf(fabsf(res[2 * i]), fabsf(res[2 * i + 1])));
             }
             const uint32_t rsb = tw::f32_to_e4m3(fmaxf(rpeak * (1.f / 6.f), 0.001953125f));
             const float inv_rs = rcp_approx(tw::e4m3_to_f32(rsb));
-            uint32_t rw[2] = {0u, 0u};
+            rw[2 * g] = rw[2 * g + 1] = 0u;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) rw[i >> 2] |= tw::f32x2_to_e2m1x2(res[2 * i] * inv_rs, res[2 * i + 1] * inv_rs) << (8 * (i & 3));
-            *reinterpret_cast<uint2*>(p0 + ATT_TILE + code_off) = make_uint2(rw[0], rw[1]);
-            sfp[ATT_SF + atom_offset(r, grp)] = (uint8_t)rsb;
+            for (int i = 0; i < 8; ++i) rw[2 * g + (i >> 2)] |= tw::f32x2_to_e2m1x2(res[2 * i] * inv_rs, res[2 * i + 1] * inv_rs) << (8 * (i & 3));
+            sf_res |= rsb << (8 * (c * 2 + g));
           }
         }
+        // K16 groups 2j and 2j + 1 of a row share one 16-byte chunk of the 64-byte-swizzled P tile
+        const int pair = half * 2 + c;
+        const uint32_t code_off = (uint32_t)r * 64u + (uint32_t)((pair ^ ((r >> 1) & 3)) << 4);
+        *reinterpret_cast<uint4*>(p0 + code_off) = make_uint4(w[0], w[1], w[2], w[3]);
+        if (rep) *reinterpret_cast<uint4*>(p0 + ATT_TILE + code_off) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
       }
-      den = den * alpha + rowsum;                             // this half's share of the denominator
+      // the four scale bytes of this half-row are contiguous in the atom layout
+      *reinterpret_cast<uint32_t*>(sfp + atom_offset(r, half * 4)) = sf_base;
+      if (rep) *reinterpret_cast<uint32_t*>(sfp + ATT_SF + atom_offset(r, half * 4)) = sf_res;
+      den = __fmaf_rn(den, alpha, zsum * pf);                 // this half's share of the denominator
       mx = nm;
       // scores consumed, kf consumed, P visible to the tensor core (async proxy)
       tw::tc_fence_before();
       tw::fence_proxy_async();
       __syncwarp();
       if (lane == 0) { tw::mbar_arrive(sEmpty + par); tw::mbar_arrive(kEmpty + s); tw::mbar_arrive(pFull + par); }
-      // T = P V of this tile: this thread accumulates channels c0 .. c0 + 63 of its row
-      ok = tw::mbar_wait(tFull, t & 1, abort_flag) && tw::mbar_wait(vFull + s, ph, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tw::tc_fence_after();
-      const float* vf = reinterpret_cast<const float*>(smem + L::OFF_VF + s * 512) + c0;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        tw::tmem_load_32x32(lane_base + TM_T + c0 + c * 32, v);
-        tw::tmem_load_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          acc[c * 32 + i] = __fmaf_rn(acc[c * 32 + i], alpha, __uint_as_float(v[i]) * pf * vf[c * 32 + i]);
-      }
-      tw::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) { tw::mbar_arrive(tEmpty); tw::mbar_arrive(vEmpty + s); }
-    }
+      return true;
+    };
+
+    const bool ragged = (p.n & 127) != 0;
+    for (int t = 0; t < p.nt && ok; ++t)
+      ok = (ragged && t == p.nt - 1) ? tile(t, std::true_type{}) : tile(t, std::false_type{});
+    if (ok && p.nt > 0) ok = accumulate(p.nt - 1, alpha_prev, pf_prev);
     // the two halves of a row add their denominators
-    xchg[half * 128 + r] = den;
+    xchg[(4 + half) * 128 + r] = den;
     asm volatile("bar.sync 1, 256;" ::: "memory");
-    den += xchg[(half ^ 1) * 128 + r];
+    den += xchg[(4 + (half ^ 1)) * 128 + r];
     if (ok && m < p.m) {
       const float inv = 1.f / den;
       __nv_bfloat16* dst = p.out + ((size_t)m * p.hq + h) * 128 + c0;
