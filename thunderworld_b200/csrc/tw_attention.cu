@@ -4,6 +4,7 @@
 //   pack_qk :12-25, pack_v :29-47, streaming_attention :51-124, select_tiles_head :191-215
 // and the per-row-factor quantizer _quantize.py:7-39 (factor = max(|row|max / 1536, 1e-12)).
 // Packing is redone for every call; nothing about old inputs is cached. P is quantized on chip.
+#include <cstdio>
 #include <type_traits>
 #include <cuda.h>
 #include "tw_common.cuh"
@@ -277,6 +278,12 @@ namespace {
 constexpr int ATT_TILE = 128 * 64;        // bytes of a 128 x 128 NVFP4 code tile
 constexpr int ATT_SF = 1024;
 constexpr int ATT_SLOTS = 3;
+constexpr int ATT_THREADS = 640;       // 4 control warps, 8 softmax warps, 8 accumulate warps
+// Register budgets per thread after the warpgroups rebalance. The launch allocates ATT_REGS_LAUNCH for each
+// of the 20 warps; a warpgroup that asks for more than the others have released waits forever, so the
+// sum is checked here.
+constexpr int ATT_REGS_LAUNCH = 96, ATT_REGS_CONTROL = 56, ATT_REGS_SOFTMAX = 104, ATT_REGS_ACCUM = 104;
+static_assert(4 * ATT_REGS_CONTROL + 8 * ATT_REGS_SOFTMAX + 8 * ATT_REGS_ACCUM <= 20 * ATT_REGS_LAUNCH, "register budgets exceed the launch allocation");
 constexpr int ATT_NT_MAX = 1024;
 
 struct AttParams {
@@ -301,9 +308,10 @@ struct AttSmem {
   static constexpr int OFF_KF = OFF_SFP + 2 * 2 * ATT_SF;           // slots x 128 floats
   static constexpr int OFF_VF = OFF_KF + ATT_SLOTS * 512;
   static constexpr int OFF_SEL = OFF_VF + ATT_SLOTS * 512;          // per key tile: bit0 QK repair, bit1 PV repair
-  static constexpr int OFF_XCHG = OFF_SEL + ATT_NT_MAX;             // 3 x 2 x 128 floats: row maxima (two parities), denominators
-  static constexpr int OFF_BAR = OFF_XCHG + 3 * 2 * 128 * 4;
-  static constexpr int NUM_BARS = 1 + 4 * ATT_SLOTS + 2 + 2 + 2 + 2 + 2;
+  static constexpr int OFF_STAT = (OFF_SEL + ATT_NT_MAX + 15) / 16 * 16;  // ring of 4 x 128 rows x (ref, pf, row sum, -)
+  static constexpr int OFF_GMAX = OFF_STAT + 4 * 128 * 16;          // 2 softmax groups x 8 K16 groups x 128 rows: group maxima
+  static constexpr int OFF_BAR = OFF_GMAX + 2 * 8 * 128 * 4;
+  static constexpr int NUM_BARS = 1 + 4 * ATT_SLOTS + 2 + 2 + 2 + 2 + 2 + 2 + 4;
   static constexpr int BYTES = OFF_BAR + NUM_BARS * 8 + 64 + 1024;
 };
 // tensor-memory columns
@@ -315,13 +323,18 @@ __device__ __forceinline__ float rcp_approx(float x) {
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
   return r;
 }
+__device__ __forceinline__ float lg2_approx(float x) {
+  float r;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
 __device__ __forceinline__ float exp2_approx(float x) {
   float r;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
   return r;
 }
 
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(ATT_THREADS, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const AttParams p) {
   using L = AttSmem;
@@ -339,7 +352,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   uint64_t* pEmpty = pFull + 2;             // [2] PV of that buffer finished
   uint64_t* tFull = pEmpty + 2;             // [1] (+1 spare) PV result ready in TMEM
   uint64_t* tEmpty = tFull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tEmpty + 2);
+  uint64_t* statFull = tEmpty + 2;          // [4] (alpha, pf) of a key tile written
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(statFull + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint8_t* sel = smem + L::OFF_SEL;
 
@@ -352,14 +366,15 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (threadIdx.x == 0) {
     tw::mbar_init(qFull, 1);
     for (int i = 0; i < ATT_SLOTS; ++i) {
-      tw::mbar_init(kFull + i, 1); tw::mbar_init(kEmpty + i, 9);   // MMA commit + 8 softmax warps (kf)
-      tw::mbar_init(vFull + i, 1); tw::mbar_init(vEmpty + i, 9);
+      tw::mbar_init(kFull + i, 1); tw::mbar_init(kEmpty + i, 5);   // MMA commit + the 4 softmax warps of the tile's group (kf)
+      tw::mbar_init(vFull + i, 1); tw::mbar_init(vEmpty + i, 9);   // MMA commit + 8 accumulate warps (vf)
     }
     for (int i = 0; i < 2; ++i) {
-      tw::mbar_init(sFull + i, 1); tw::mbar_init(sEmpty + i, 8);
-      tw::mbar_init(pFull + i, 8); tw::mbar_init(pEmpty + i, 1);
+      tw::mbar_init(sFull + i, 1); tw::mbar_init(sEmpty + i, 4);
+      tw::mbar_init(pFull + i, 4); tw::mbar_init(pEmpty + i, 1);
       tw::mbar_init(tFull + i, 1); tw::mbar_init(tEmpty + i, 8);
     }
+    for (int i = 0; i < 4; ++i) tw::mbar_init(statFull + i, 4);
     *abort_flag = 0;
     tw::fence_barrier_init();
     tw::tma_prefetch_desc(&tm_q); tw::tma_prefetch_desc(&tm_k); tw::tma_prefetch_desc(&tm_v);
@@ -377,6 +392,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   tw::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
+  if (warp < 4) {
+  tw::reg_budget_shrink<ATT_REGS_CONTROL>();
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
@@ -484,96 +501,73 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         tw::tc_commit(pEmpty + par);
       }
     }
-  } else if (warp >= 4) {
-    // ------------------------------------------------------------------ softmax, P quantization, accumulate
-    // Eight warps: two per TMEM lane quadrant. A thread owns one query row and one half of the
-    // 128 columns (keys for S and P, channels for T and the accumulator); the two halves of a row
-    // exchange their partial row maximum through shared memory once per key tile.
-    // Everything runs in the log2 domain: x = S * kf[n] * (qf[m] * log2(e) / sqrt(128)). The scaled
-    // probability z = p / pf is produced directly as exp2(x - off) with off = nm + log2(pf), and
-    // pf = max(exp2(rowmax - nm) / 1536, 1e-12) is  exp2(off - nm)  with
-    // off = max(rowmax - log2(1536), nm + log2(1e-12)).
-    // The accumulation of P V of tile t is deferred until the scores of tile t + 1 have been reduced,
-    // so the P V product runs under the next tile's softmax instead of stalling these warps.
-    const int quad = warp & 3, half = (warp - 4) >> 2, r = quad * 32 + lane;
-    const int m = mb * 128 + r, c0 = half * 64;
+  }
+  } else if (warp < 12) {
+    // ------------------------------------------------------------------ softmax and P quantization
+    // Two groups of four warps; group g takes the key tiles of parity g (their scores live in S[g], their
+    // probabilities in P[g]), so the two warps of every scheduler work on different tiles and the
+    // conversion-unit-bound second pass of one runs beside the first pass and the waits of the other.
+    // A thread owns one query row (TMEM lane) with all 128 key columns of the tile.
+    // Everything runs in the log2 domain: x = S * kf[n] * (qf[m] * log2(e) / sqrt(128)). Each group keeps
+    // its own lazy reference ref (raised only when a tile's row maximum exceeds it by more than 2^8);
+    // the scaled probability z = p / pf is produced directly as exp2(x - off) with off = ref + log2(pf):
+    // pf = max(exp2(rowmax - ref) / 1536, 1e-12) = exp2(off - ref),
+    // off = max(rowmax - log2(1536), ref + log2(1e-12)).
+    // (ref, pf, row sum) of each tile go to the accumulate warps through a ring of four slots.
+    tw::reg_budget_grow<ATT_REGS_SOFTMAX>();
+    const int quad = warp & 3, grp = (warp - 4) >> 2, r = quad * 32 + lane;
+    const int m = mb * 128 + r;
     const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
     const float qfl = (m < p.mp ? __ldg(p.qf + (size_t)h * p.mp + m) : 1.f) * (0.08838834764831845f * 1.4426950408889634f);
-    float* xchg = reinterpret_cast<float*>(smem + L::OFF_XCHG);       // [3][2][128]: row maxima by tile parity, then denominators; half, row
-    float acc[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) acc[i] = 0.f;
-    float mx = -INFINITY, den = 0.f;                                   // running maximum (log2 domain), denominator share
-    float alpha_prev = 1.f, pf_prev = 0.f;
+    float4* stats = reinterpret_cast<float4*>(smem + L::OFF_STAT);    // [4][128]: (ref, pf, row sum, -)
+    float ref = -INFINITY;
     bool ok = true;
-
-    // acc = acc * alpha + T * pf * vf for key tile u (channels c0 .. c0 + 63 of this row)
-    auto accumulate = [&](int u, float alpha, float pf) {
-      const uint32_t s = u % ATT_SLOTS, ph = (u / ATT_SLOTS) & 1;
-      bool good = tw::mbar_wait(tFull, u & 1, abort_flag) && tw::mbar_wait(vFull + s, ph, abort_flag);
-      good = __all_sync(0xffffffffu, good);
-      if (!good) return false;
-      tw::tc_fence_after();
-      const float4* vf = reinterpret_cast<const float4*>(smem + L::OFF_VF + s * 512) + (c0 >> 2);
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        tw::tmem_load_32x32(lane_base + TM_T + c0 + c * 32, v);
-        tw::tmem_load_wait();
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float4 f = vf[c * 8 + i];
-          acc[c * 32 + 4 * i + 0] = __fmaf_rn(acc[c * 32 + 4 * i + 0], alpha, __uint_as_float(v[4 * i + 0]) * (pf * f.x));
-          acc[c * 32 + 4 * i + 1] = __fmaf_rn(acc[c * 32 + 4 * i + 1], alpha, __uint_as_float(v[4 * i + 1]) * (pf * f.y));
-          acc[c * 32 + 4 * i + 2] = __fmaf_rn(acc[c * 32 + 4 * i + 2], alpha, __uint_as_float(v[4 * i + 2]) * (pf * f.z));
-          acc[c * 32 + 4 * i + 3] = __fmaf_rn(acc[c * 32 + 4 * i + 3], alpha, __uint_as_float(v[4 * i + 3]) * (pf * f.w));
-        }
-      }
-      tw::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) { tw::mbar_arrive(tEmpty); tw::mbar_arrive(vEmpty + s); }
-      return true;
+    // four code bytes (one per register, upper bits clear) -> one word, first byte lowest
+    auto pack4 = [](uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) {
+      return __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
     };
-
-    // one key tile; TAIL: the tile holds padding columns (only the last tile of a ragged key length)
-    auto tile = [&](int t, auto tail_tag) {
+    // One key tile. TAIL: the tile holds padding columns (only the last tile of a ragged key length);
+    // REP: the residual plane P1 is produced too. The loops over the four 32-column chunks stay rolled:
+    // the body of a chunk is a few kilobytes of straight-line code and is reused from the instruction
+    // cache, where the fully unrolled tile was refetched by every warp for every tile.
+    float* gsm = reinterpret_cast<float*>(smem + L::OFF_GMAX) + grp * 8 * 128;   // [8 K16 groups][128 rows]
+    auto tile = [&](int t, auto tail_tag, auto rep_tag) {
       constexpr bool TAIL = decltype(tail_tag)::value;
-      const uint32_t s = t % ATT_SLOTS, ph = (t / ATT_SLOTS) & 1, par = t & 1;
-      const bool rep = sel[t] & 2;
+      constexpr bool REP = decltype(rep_tag)::value;
+      const uint32_t s = t % ATT_SLOTS, ph = (t / ATT_SLOTS) & 1, par = grp;
       bool good = tw::mbar_wait(sFull + par, (t >> 1) & 1, abort_flag) && tw::mbar_wait(kFull + s, ph, abort_flag);
       good = __all_sync(0xffffffffu, good);
       if (!good) return false;
       tw::tc_fence_after();
-      const float4* kf = reinterpret_cast<const float4*>(smem + L::OFF_KF + s * 512) + (c0 >> 2);
-      const int n_valid = p.n - t * 128 - c0;                 // columns >= n_valid of this half are padding
-      // pass 1: row maximum of S * kf over this half, the other half's through shared memory
+      const float4* kf = reinterpret_cast<const float4*>(smem + L::OFF_KF + s * 512);
+      const int n_valid = p.n - t * 128;                      // columns >= n_valid are padding
+      // pass 1: maximum of S * kf per K16 group
       float rowmax = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
-        tw::tmem_load_32x32(lane_base + TM_S + par * 128 + c0 + c * 32, v);
+        tw::tmem_load_32x32(lane_base + TM_S + par * 128 + c * 32, v);
         tw::tmem_load_wait();
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float4 f = kf[c * 8 + i];
-          const float e[4] = {__uint_as_float(v[4 * i]) * f.x, __uint_as_float(v[4 * i + 1]) * f.y,
-                              __uint_as_float(v[4 * i + 2]) * f.z, __uint_as_float(v[4 * i + 3]) * f.w};
+        for (int g = 0; g < 2; ++g) {
+          float best = -INFINITY;
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            rowmax = fmaxf(rowmax, (!TAIL || (c * 32 + 4 * i + j) < n_valid) ? e[j] : -INFINITY);
+          for (int i = 0; i < 4; ++i) {
+            const float4 f = kf[c * 8 + g * 4 + i];
+            const float e[4] = {__uint_as_float(v[g * 16 + 4 * i]) * f.x, __uint_as_float(v[g * 16 + 4 * i + 1]) * f.y,
+                                __uint_as_float(v[g * 16 + 4 * i + 2]) * f.z, __uint_as_float(v[g * 16 + 4 * i + 3]) * f.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              best = fmaxf(best, (!TAIL || (c * 32 + g * 16 + 4 * i + j) < n_valid) ? e[j] : -INFINITY);
+          }
+          gsm[(c * 2 + g) * 128 + r] = best;
+          rowmax = fmaxf(rowmax, best);
         }
       }
       rowmax *= qfl;                                          // qfl > 0
-      xchg[(par * 2 + half) * 128 + r] = rowmax;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      rowmax = fmaxf(rowmax, xchg[(par * 2 + (half ^ 1)) * 128 + r]);
-      const float nm = fmaxf(mx, rowmax);
-      const float alpha = exp2_approx(mx - nm);
-      const float off = fmaxf(rowmax - 10.584962500721156f, nm - 39.863137138648348f);
-      const float pf = exp2_approx(off - nm);
-      // deferred accumulation of the previous tile: its P V product had this tile's first pass to finish
-      if (t > 0 && !accumulate(t - 1, alpha_prev, pf_prev)) return false;
-      alpha_prev = alpha; pf_prev = pf;
+      if (rowmax > ref + 8.f) ref = rowmax;                   // lazy reference
+      const float off = fmaxf(rowmax - 10.584962500721156f, ref - 39.863137138648348f);
+      const float pf = exp2_approx(off - ref);
       // the P buffer of this parity must have been consumed by the PV product two tiles ago
       good = tw::mbar_wait(pEmpty + par, ((t >> 1) & 1) ^ 1, abort_flag);
       good = __all_sync(0xffffffffu, good);
@@ -582,17 +576,27 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       uint8_t* sfp = smem + L::OFF_SFP + par * 2 * ATT_SF;
       float zsum = 0.f;
       uint32_t sf_base = 0u, sf_res = 0u;
-      // pass 2: scaled probabilities, their NVFP4 codes and scales, 32 columns at a time
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      // pass 2: per K16 group the E4M3 scale follows from the group maximum, and the codes are the E2M1
+      // roundings of y = exp2(x - off - log2(scale)) = z / scale
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
-        tw::tmem_load_32x32(lane_base + TM_S + par * 128 + c0 + c * 32, v);
+        tw::tmem_load_32x32(lane_base + TM_S + par * 128 + c * 32, v);
         tw::tmem_load_wait();
+        if (c == 3) {                                         // scores are in registers: release S[par]
+          tw::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) tw::mbar_arrive(sEmpty + par);
+        }
         uint32_t w[4], rw[4];
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
-          float z[16];
-          float peak = 0.f;
+          const float peak = exp2_approx(__fmaf_rn(gsm[(c * 2 + g) * 128 + r], qfl, -off));
+          const uint32_t sb = tw::f32_to_e4m3(fmaxf(peak * (1.f / 6.f), 0.001953125f));
+          const float sv = tw::e4m3_to_f32(sb);
+          const float offg = off + lg2_approx(sv);
+          float y[16];
+          float ysum = 0.f;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float4 f = kf[c * 8 + g * 4 + i];
@@ -600,64 +604,122 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                                 __uint_as_float(v[g * 16 + 4 * i + 2]) * f.z, __uint_as_float(v[g * 16 + 4 * i + 3]) * f.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              float zz = exp2_approx(__fmaf_rn(e[j], qfl, -off));
-              if (TAIL && (c * 32 + g * 16 + 4 * i + j) >= n_valid) zz = 0.f;
-              z[4 * i + j] = zz;
-              zsum += zz;
-              peak = fmaxf(peak, zz);
+              float yy = exp2_approx(__fmaf_rn(e[j], qfl, -offg));
+              if (TAIL && (c * 32 + g * 16 + 4 * i + j) >= n_valid) yy = 0.f;
+              y[4 * i + j] = yy;
+              ysum += yy;
             }
           }
-          const uint32_t sb = tw::f32_to_e4m3(fmaxf(peak * (1.f / 6.f), 0.001953125f));
-          const float sv = tw::e4m3_to_f32(sb), inv_s = rcp_approx(sv);
-          w[2 * g] = w[2 * g + 1] = 0u;
+          zsum = __fmaf_rn(ysum, sv, zsum);
+          uint32_t b[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) w[2 * g + (i >> 2)] |= tw::f32x2_to_e2m1x2(z[2 * i] * inv_s, z[2 * i + 1] * inv_s) << (8 * (i & 3));
-          sf_base |= sb << (8 * (c * 2 + g));
-          if (rep) {
-            float res[16];
+          for (int i = 0; i < 8; ++i) b[i] = tw::f32x2_to_e2m1x2(y[2 * i], y[2 * i + 1]);
+          w[2 * g] = pack4(b[0], b[1], b[2], b[3]);
+          w[2 * g + 1] = pack4(b[4], b[5], b[6], b[7]);
+          sf_base |= sb << (8 * ((c & 1) * 2 + g));
+          if (REP) {
+            // residual in units of the base scale: res = y - value(code); its scale is sv * max|res| / 6
             float rpeak = 0.f;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const float2 val = e2m1x2_values((w[2 * g + (i >> 2)] >> (8 * (i & 3))) & 0xffu);
-              res[2 * i] = __fmaf_rn(-val.x, sv, z[2 * i]);
-              res[2 * i + 1] = __fmaf_rn(-val.y, sv, z[2 * i + 1]);
-              rpeak = fmaxf(rpeak, fmaxf(fabsf(res[2 * i]), fabsf(res[2 * i + 1])));
+              const float2 val = e2m1x2_values(b[i]);
+              y[2 * i] -= val.x;
+              y[2 * i + 1] -= val.y;
+              rpeak = fmaxf(rpeak, fmaxf(fabsf(y[2 * i]), fabsf(y[2 * i + 1])));
             }
-            const uint32_t rsb = tw::f32_to_e4m3(fmaxf(rpeak * (1.f / 6.f), 0.001953125f));
-            const float inv_rs = rcp_approx(tw::e4m3_to_f32(rsb));
-            rw[2 * g] = rw[2 * g + 1] = 0u;
+            const uint32_t rsb = tw::f32_to_e4m3(fmaxf(rpeak * sv * (1.f / 6.f), 0.001953125f));
+            const float mult = sv * rcp_approx(tw::e4m3_to_f32(rsb));
 #pragma unroll
-            for (int i = 0; i < 8; ++i) rw[2 * g + (i >> 2)] |= tw::f32x2_to_e2m1x2(res[2 * i] * inv_rs, res[2 * i + 1] * inv_rs) << (8 * (i & 3));
-            sf_res |= rsb << (8 * (c * 2 + g));
+            for (int i = 0; i < 8; ++i) b[i] = tw::f32x2_to_e2m1x2(y[2 * i] * mult, y[2 * i + 1] * mult);
+            rw[2 * g] = pack4(b[0], b[1], b[2], b[3]);
+            rw[2 * g + 1] = pack4(b[4], b[5], b[6], b[7]);
+            sf_res |= rsb << (8 * ((c & 1) * 2 + g));
           }
         }
-        // K16 groups 2j and 2j + 1 of a row share one 16-byte chunk of the 64-byte-swizzled P tile
-        const int pair = half * 2 + c;
-        const uint32_t code_off = (uint32_t)r * 64u + (uint32_t)((pair ^ ((r >> 1) & 3)) << 4);
+        // K16 groups 2c and 2c + 1 of a row share one 16-byte chunk of the 64-byte-swizzled P tile
+        const uint32_t code_off = (uint32_t)r * 64u + (uint32_t)((c ^ ((r >> 1) & 3)) << 4);
         *reinterpret_cast<uint4*>(p0 + code_off) = make_uint4(w[0], w[1], w[2], w[3]);
-        if (rep) *reinterpret_cast<uint4*>(p0 + ATT_TILE + code_off) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+        if (REP) *reinterpret_cast<uint4*>(p0 + ATT_TILE + code_off) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+        if (c & 1) {                                          // four scale bytes of the row: one word of the atom layout
+          *reinterpret_cast<uint32_t*>(sfp + atom_offset(r, (c >> 1) * 4)) = sf_base;
+          if (REP) *reinterpret_cast<uint32_t*>(sfp + ATT_SF + atom_offset(r, (c >> 1) * 4)) = sf_res;
+          sf_base = sf_res = 0u;
+        }
       }
-      // the four scale bytes of this half-row are contiguous in the atom layout
-      *reinterpret_cast<uint32_t*>(sfp + atom_offset(r, half * 4)) = sf_base;
-      if (rep) *reinterpret_cast<uint32_t*>(sfp + ATT_SF + atom_offset(r, half * 4)) = sf_res;
-      den = __fmaf_rn(den, alpha, zsum * pf);                 // this half's share of the denominator
-      mx = nm;
-      // scores consumed, kf consumed, P visible to the tensor core (async proxy)
-      tw::tc_fence_before();
+      stats[(t & 3) * 128 + r] = make_float4(ref, pf, zsum * pf, 0.f);
+      // P visible to the tensor core (async proxy); key factors consumed
       tw::fence_proxy_async();
       __syncwarp();
-      if (lane == 0) { tw::mbar_arrive(sEmpty + par); tw::mbar_arrive(kEmpty + s); tw::mbar_arrive(pFull + par); }
+      if (lane == 0) { tw::mbar_arrive(kEmpty + s); tw::mbar_arrive(pFull + par); tw::mbar_arrive(statFull + (t & 3)); }
       return true;
     };
-
     const bool ragged = (p.n & 127) != 0;
-    for (int t = 0; t < p.nt && ok; ++t)
-      ok = (ragged && t == p.nt - 1) ? tile(t, std::true_type{}) : tile(t, std::false_type{});
-    if (ok && p.nt > 0) ok = accumulate(p.nt - 1, alpha_prev, pf_prev);
-    // the two halves of a row add their denominators
-    xchg[(4 + half) * 128 + r] = den;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    den += xchg[(4 + (half ^ 1)) * 128 + r];
+    for (int t = grp; t < p.nt && ok; t += 2) {
+      const bool rep = sel[t] & 2;
+      if (ragged && t == p.nt - 1) ok = rep ? tile(t, std::true_type{}, std::true_type{}) : tile(t, std::true_type{}, std::false_type{});
+      else ok = rep ? tile(t, std::false_type{}, std::true_type{}) : tile(t, std::false_type{}, std::false_type{});
+    }
+  } else {
+    // ------------------------------------------------------------------ accumulate and output
+    // Eight warps, two per TMEM lane quadrant: a thread owns one query row and 64 of the 128 channels.
+    // Per key tile, with (ref, pf, sum) of the row from the softmax group that handled it:
+    //   R' = ref if ref > R + 2^8 else R;  alpha = 2^(R - R');  w = 2^(ref - R')
+    //   acc = acc * alpha + T * (pf * w) * vf;   den = den * alpha + sum * w
+    // fp32, in registers; the rescaling multiply is skipped when alpha is 1 for the whole warp.
+    tw::reg_budget_grow<ATT_REGS_ACCUM>();
+    const int quad = warp & 3, half = (warp - 12) >> 2, r = quad * 32 + lane;
+    const int m = mb * 128 + r, c0 = half * 64;
+    const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
+    const float4* stats = reinterpret_cast<const float4*>(smem + L::OFF_STAT);
+    float acc[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+    float R = -INFINITY, den = 0.f;
+    bool ok = true;
+    for (int t = 0; t < p.nt && ok; ++t) {
+      const uint32_t s = t % ATT_SLOTS, ph = (t / ATT_SLOTS) & 1;
+      ok = tw::mbar_wait(statFull + (t & 3), (t >> 2) & 1, abort_flag) && tw::mbar_wait(tFull, t & 1, abort_flag) &&
+           tw::mbar_wait(vFull + s, ph, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const float4 st = stats[(t & 3) * 128 + r];
+      const float Rn = st.x > R + 8.f ? st.x : R;
+      const float alpha = exp2_approx(R - Rn), wgt = exp2_approx(st.x - Rn);
+      const float pf = st.y * wgt;
+      den = __fmaf_rn(den, alpha, st.z * wgt);
+      R = Rn;
+      const bool keep = __all_sync(0xffffffffu, alpha == 1.f);
+      tw::tc_fence_after();
+      const float4* vf = reinterpret_cast<const float4*>(smem + L::OFF_VF + s * 512) + (c0 >> 2);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[16];
+        tw::tmem_load_32x32_x16(lane_base + TM_T + c0 + c * 16, v);
+        tw::tmem_load_wait();
+        if (keep) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float4 f = vf[c * 4 + i];
+            acc[c * 16 + 4 * i + 0] = __fmaf_rn(__uint_as_float(v[4 * i + 0]) * f.x, pf, acc[c * 16 + 4 * i + 0]);
+            acc[c * 16 + 4 * i + 1] = __fmaf_rn(__uint_as_float(v[4 * i + 1]) * f.y, pf, acc[c * 16 + 4 * i + 1]);
+            acc[c * 16 + 4 * i + 2] = __fmaf_rn(__uint_as_float(v[4 * i + 2]) * f.z, pf, acc[c * 16 + 4 * i + 2]);
+            acc[c * 16 + 4 * i + 3] = __fmaf_rn(__uint_as_float(v[4 * i + 3]) * f.w, pf, acc[c * 16 + 4 * i + 3]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float4 f = vf[c * 4 + i];
+            acc[c * 16 + 4 * i + 0] = __fmaf_rn(__uint_as_float(v[4 * i + 0]) * f.x, pf, acc[c * 16 + 4 * i + 0] * alpha);
+            acc[c * 16 + 4 * i + 1] = __fmaf_rn(__uint_as_float(v[4 * i + 1]) * f.y, pf, acc[c * 16 + 4 * i + 1] * alpha);
+            acc[c * 16 + 4 * i + 2] = __fmaf_rn(__uint_as_float(v[4 * i + 2]) * f.z, pf, acc[c * 16 + 4 * i + 2] * alpha);
+            acc[c * 16 + 4 * i + 3] = __fmaf_rn(__uint_as_float(v[4 * i + 3]) * f.w, pf, acc[c * 16 + 4 * i + 3] * alpha);
+          }
+        }
+      }
+      tw::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { tw::mbar_arrive(tEmpty); tw::mbar_arrive(vEmpty + s); }
+    }
     if (ok && m < p.m) {
       const float inv = 1.f / den;
       __nv_bfloat16* dst = p.out + ((size_t)m * p.hq + h) * 128 + c0;
@@ -784,8 +846,11 @@ extern "C" int tw_attention(const TwAttentionArgs* a, void* stream_) {
   if (!configured) {
     if (cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttSmem::BYTES) != cudaSuccess)
       return TW_ERR_LAUNCH;
+    // the in-kernel register rebalance assumes the launch allocation it was sized for
+    cudaFuncAttributes attr;
+    if (cudaFuncGetAttributes(&attr, attention_kernel) != cudaSuccess || attr.numRegs < ATT_REGS_LAUNCH) return TW_ERR_LAUNCH;
     configured = true;
   }
-  attention_kernel<<<dim3((a->m + 127) / 128, a->hq), 384, AttSmem::BYTES, static_cast<cudaStream_t>(stream_)>>>(tm_q, tm_k, tm_v, p);
+  attention_kernel<<<dim3((a->m + 127) / 128, a->hq), ATT_THREADS, AttSmem::BYTES, static_cast<cudaStream_t>(stream_)>>>(tm_q, tm_k, tm_v, p);
   return cudaGetLastError() == cudaSuccess ? TW_OK : TW_ERR_LAUNCH;
 }
