@@ -156,6 +156,31 @@ typedef struct TwAttentionArgs {
 size_t tw_attention_workspace(int m, int n, int hq, int hk);
 int tw_attention(const TwAttentionArgs* args, void* stream);
 
+/* ---- pointwise producers with fused tensor factor ------------------------------------------
+ * Each writes its bf16 result once and, when `stats` is given, reduces max|y| in the same pass:
+ * stats[0] = factor = max|y| / 2688 (1.0 for an all-zero tensor, thunderworld_fp4/_linear_kernels.py:17-19
+ * finish_amax), stats[1] = max|y|. The factor feeds tw_quantize with factor_given, which then skips its own
+ * reduction pass (the reference's pack_with_factor, thunderworld_fp4/_fusion.py:37-42).
+ * `scratch`: 8 bytes of device memory, zeroed once by the caller; every call leaves it zeroed. Calls that
+ * share a scratch must not overlap on the GPU. */
+enum { TW_ACT_RELU2 = 0, TW_ACT_MUL = 1, TW_ACT_GELU_TANH = 2 };
+/* y = bf16(relu(a)^2) | bf16(a * b) | bf16(gelu_tanh(a)); fp32 arithmetic, one rounding. n % 8 == 0.
+ * Modes 0 and 1 replace pointwise_amax / activate_with_factor (thunderworld_fp4/_fusion.py:15-34) and are
+ * bit-exact against them; mode 2 is the activation of the DiT step's FFN. */
+int tw_activate(const void* a, const void* b, void* y, float* stats, void* scratch, long long n, int mode, void* stream);
+/* y[r, :] = bf16( x[r, :] * rsqrt(mean(x[r, :]^2) + eps) [* weight] [* (1 + scale[b, :]) + shift[b, :]] ), b = r /
+ * rows_per_batch. weight, shift, scale: bf16 or NULL (shift and scale together). Replaces nemotron_norm
+ * (thunderworld_fp4/cosmos/norm_fusion.py:23-43) plus the AdaLN modulation that follows it in a DiT block.
+ * hidden % 8 == 0, hidden <= 16384. */
+int tw_rms_norm(const void* x, const void* weight, const void* shift, const void* scale, void* y, float* stats,
+                void* scratch, int rows, int hidden, int rows_per_batch, float eps, void* stream);
+/* RMSNorm over the last dimension (128) of a strided bf16 view [tokens, heads, 128] (query / key norm);
+ * y is contiguous [tokens, heads, 128]. Strides in elements, multiples of 8. */
+int tw_rms_norm_heads(const void* x, void* y, long long tokens, int heads, long long stride_token, long long stride_head,
+                      float eps, void* stream);
+/* x[r, :] = bf16(x[r, :] + gate[r / rows_per_batch, :] * y[r, :]) in place (gated residual of a DiT block). */
+int tw_gate_residual(void* x, const void* gate, const void* y, int rows, int hidden, int rows_per_batch, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

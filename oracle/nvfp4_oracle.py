@@ -458,3 +458,49 @@ def select_tiles(q, k, v, counts, terms=3):
             order = sorted(range(nt), key=lambda j: (-sc[j], j))
             flags[head, b, order[:counts[head]]] = terms
     return flags, scores
+
+
+# ----------------------------------------------------------------------------
+# Pointwise producers with fused tensor factor
+# ----------------------------------------------------------------------------
+def finish_factor(y):
+    """finish_amax (_linear_kernels.py:17-19): max|y| / 2688, or 1 for an all-zero tensor."""
+    top = F32(np.abs(y).max()) if y.size else F32(0)
+    return F32(top / F32(2688.)) if top > 0 else F32(1.)
+
+
+def activate_with_factor(a, b=None, mode=None):
+    """pointwise_amax / activate_with_factor (_fusion.py:15-34): relu(a)^2 or a*b in float32, one bf16
+    rounding, factor from the rounded values. mode 'gelu_tanh' (not in the reference) is evaluated in
+    float64 and rounded once. a, b: bf16 values held in float32 arrays."""
+    a = np.asarray(a, F32)
+    if mode == 'gelu_tanh':
+        x = a.astype(np.float64)
+        y = 0.5 * x * (1. + np.tanh(0.7978845608028654 * (x + 0.044715 * x ** 3)))
+        y = bf16_round(y.astype(F32))
+    elif b is None:
+        t = np.maximum(a, F32(0))
+        y = bf16_round(t * t)
+    else:
+        y = bf16_round(a * np.asarray(b, F32))
+    return y, finish_factor(y)
+
+
+def rms_norm(x, weight=None, eps=1e-6, shift=None, scale=None):
+    """nemotron_norm (cosmos/norm_fusion.py:23-43) with an optional AdaLN modulation, evaluated in float64
+    and rounded to bf16 once. x [batch, tokens, hidden]; shift, scale [batch, hidden]."""
+    xf = np.asarray(x, np.float64)
+    y = xf / np.sqrt((xf ** 2).mean(-1, keepdims=True) + eps)
+    if weight is not None:
+        y = y * np.asarray(weight, np.float64)
+    if scale is not None:
+        y = y * (1. + np.asarray(scale, np.float64)[:, None]) + np.asarray(shift, np.float64)[:, None]
+    y = bf16_round(y.astype(F32))
+    return y, finish_factor(y)
+
+
+def gate_residual(x, gate, y):
+    """bf16(x + gate[:, None] * y): the product of two bf16 values and its sum with a third are exact in
+    float64 for magnitudes of interest, so float32 then bf16 rounding reproduces a float32 fma."""
+    exact = np.asarray(x, np.float64) + np.asarray(gate, np.float64)[:, None] * np.asarray(y, np.float64)
+    return bf16_round(exact.astype(F32))

@@ -85,6 +85,10 @@ def load():
         getattr(lib, name).argtypes = [ctypes.POINTER(args), _vp]
         getattr(lib, name).restype = _i
     lib.tw_attention_workspace.argtypes = [_i] * 4; lib.tw_attention_workspace.restype = ctypes.c_size_t
+    lib.tw_activate.argtypes = [_vp] * 5 + [_ll, _i, _vp]; lib.tw_activate.restype = _i
+    lib.tw_rms_norm.argtypes = [_vp] * 7 + [_i] * 3 + [ctypes.c_float, _vp]; lib.tw_rms_norm.restype = _i
+    lib.tw_rms_norm_heads.argtypes = [_vp, _vp, _ll, _i, _ll, _ll, ctypes.c_float, _vp]; lib.tw_rms_norm_heads.restype = _i
+    lib.tw_gate_residual.argtypes = [_vp] * 3 + [_i] * 3 + [_vp]; lib.tw_gate_residual.restype = _i
     _lib = lib
     return lib
 
@@ -97,4 +101,4 @@ def check(status):
 EXPORTS = ('tw_status', 'tw_abi_version', 'tw_quantize_workspace', 'tw_quantize', 'tw_quantize_static',
            'tw_quantize_static_max_tiles', 'tw_swizzle_scales',
            'tw_workspace', 'tw_fused', 'tw_fused_tile_n', 'tw_pack_rows', 'tw_select_tiles', 'tw_attention',
-           'tw_attention_workspace')
+           'tw_attention_workspace', 'tw_activate', 'tw_rms_norm', 'tw_rms_norm_heads', 'tw_gate_residual')

@@ -3,8 +3,10 @@ AdaLN modulation -> QKV (repaired linear) -> per-head RMSNorm -> FP4 attention -
 residual -> RMSNorm -> AdaLN -> FFN-up (GELU) -> FFN-down -> gated residual.
 
 The reference runs the diffusers Cosmos3 transformer (absent here); its per-layer dataflow is the one
-spelled out in thunderworld_fp4/cosmos/ar_cache.py:72-107. Norms, modulation and GELU are plain torch
-ops; every projection is a `RepairLinear`, attention goes through the engine's `attend`.
+spelled out in thunderworld_fp4/cosmos/ar_cache.py:72-107. Every projection is a `RepairLinear`, attention
+goes through the engine's `attend`; norms, modulation, GELU and the gated residuals are the fused
+pointwise producers of `ops` (one pass each, the tensor factor of the next quantizer reduced in the same
+pass, as the reference does with activate_with_factor / pack_with_factor, thunderworld_fp4/_fusion.py:26-42).
 
 Tensor parallelism: QKV and FFN-up are column-split (heads shard with them, attention needs no
 exchange); out-proj and FFN-down are row-split, their activations are quantized under the global
@@ -12,7 +14,7 @@ factor (4-byte MAX all-reduce) and their partial outputs summed with one all-red
 """
 from dataclasses import dataclass
 import torch
-from .. import parallel
+from .. import ops, parallel
 from .linears import RepairLinear
 from .settings import LinearSpec
 
@@ -47,6 +49,7 @@ class _Source:
 
 
 def rms_norm(x, eps=1e-6):
+    """Plain torch RMSNorm (reference arithmetic for tests; the model runs ops.rms_norm)."""
     xf = x.float()
     return (xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)).to(x.dtype)
 
@@ -94,26 +97,31 @@ class DiTBlock(torch.nn.Module):
             return qkv_map
         return lambda ids: parallel.remap_tiles(ids, nb, kb, tp, r, split)
 
-    def _row_split(self, layer, x):
-        """Row-split linear: global activation factor, local GEMM, summed partial outputs."""
+    def _row_split(self, layer, x, stats=None):
+        """Row-split linear: global activation factor, local GEMM, summed partial outputs.
+        stats = (factor, max|x|) of the local shard when its producer reduced them."""
         if self.topo.tp_size == 1:
-            return layer(x)
-        factor = parallel.global_factor(x, self.topo)
+            return layer(x) if stats is None else layer(x, factor=stats[0])
+        if stats is None:
+            factor = parallel.global_factor(x, self.topo)
+        else:
+            factor = parallel.global_factor_from_peak(stats[1:2].clone(), self.topo)
         return parallel.allreduce_sum(layer(x, factor=factor), self.topo)
 
     def forward(self, x, mod):
+        """x bf16 [batch, tokens, hidden], updated in place; mod [6, batch, hidden] contiguous."""
         b, s, h = x.shape
-        shift1, scale1, gate1, shift2, scale2, gate2 = mod.unbind(1)
-        y = rms_norm(x) * (1 + scale1[:, None]) + shift1[:, None]
-        qkv = self.qkv(y).reshape(b, s, 3, self.local_heads, 128)
+        shift1, scale1, gate1, shift2, scale2, gate2 = mod.unbind(0)
+        y, f = ops.rms_norm(x, shift=shift1, scale=scale1, want_factor=True)
+        qkv = self.qkv(y, factor=f).reshape(b, s, 3, self.local_heads, 128)
         q, k, v = qkv.unbind(2)
         if self.cfg.qk_norm:
-            q, k = rms_norm(q), rms_norm(k)
+            q, k = ops.rms_norm_heads(q), ops.rms_norm_heads(k)
         a = self.controller.attend(self.index, q, k, v).reshape(b, s, self.local_heads * 128)
-        x = x + gate1[:, None] * self._row_split(self.out, a)
-        y = rms_norm(x) * (1 + scale2[:, None]) + shift2[:, None]
-        u = torch.nn.functional.gelu(self.up(y), approximate='tanh')
-        return x + gate2[:, None] * self._row_split(self.down, u)
+        ops.gate_residual_(x, gate1, self._row_split(self.out, a))
+        y, f = ops.rms_norm(x, shift=shift2, scale=scale2, want_factor=True)
+        u, stats = ops.activate_with_factor(self.up(y, factor=f), mode='gelu_tanh', return_stats=True)
+        return ops.gate_residual_(x, gate2, self._row_split(self.down, u, stats))
 
 
 class DiTModel(torch.nn.Module):
@@ -125,6 +133,8 @@ class DiTModel(torch.nn.Module):
 
     def forward(self, x, mod):
         """x bf16 [batch, tokens, hidden]; mod bf16 [batch, blocks, 6, hidden] (AdaLN shift/scale/gate)."""
+        x = x.clone()                                         # blocks update the residual stream in place
+        mods = mod.permute(1, 2, 0, 3).contiguous()           # [blocks, 6, batch, hidden]
         for i, block in enumerate(self.blocks):
-            x = block(x, mod[:, i])
-        return rms_norm(x)
+            x = block(x, mods[i])
+        return ops.rms_norm(x)

@@ -153,3 +153,94 @@ def device_status(device=None):
     dev = torch.device('cuda', torch.cuda.current_device()) if device is None else device
     ws = _workspaces.get((dev, 'g'))
     return 0 if ws is None else int(ws[:4].view(torch.int32).item())
+
+
+# ---- pointwise producers with fused tensor factor -----------------------------------------------
+# Host mirrors of activate_with_factor (thunderworld_fp4/_fusion.py:26-34) and nemotron_norm
+# (thunderworld_fp4/cosmos/norm_fusion.py:29-43); same argument checks and error types.
+ACT_MODES = {'relu2': 0, 'mul': 1, 'gelu_tanh': 2}
+
+
+def _check_bf16(*tensors):
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise ValueError('expected contiguous CUDA BF16 tensors')
+
+
+def _stats(device, want):
+    """(stats[2] float32, scratch) or (None, None). The scratch word pair is zeroed once per device."""
+    if not want:
+        return None, None
+    return torch.empty(2, device=device, dtype=torch.float32), _workspace(device, 8, 'pointwise')
+
+
+def activate_with_factor(a, b=None, *, mode=None, want_factor=True, return_stats=False):
+    """y = relu(a)^2 (b None), a * b, or gelu_tanh(a) (mode='gelu_tanh'); returns (y, factor) with
+    factor = max|y| / 2688 as a 0-d float32 tensor (or None); return_stats: the pair (factor, max|y|) instead."""
+    if torch.is_grad_enabled() and (a.requires_grad or (b is not None and b.requires_grad)):
+        raise RuntimeError('fused activations are inference only')
+    _check_bf16(a, b)
+    if b is not None and b.shape != a.shape:
+        raise ValueError('operands must have equal shapes')
+    require_sm100(a.device)
+    mode = ACT_MODES[mode or ('relu2' if b is None else 'mul')]
+    y = torch.empty_like(a)
+    stats, scratch = _stats(a.device, want_factor)
+    _lib.check(_lib.load().tw_activate(_ptr(a), _ptr(b), _ptr(y), _ptr(stats), _ptr(scratch), a.numel(), mode, _stream(a.device)))
+    return y, (None if stats is None else (stats if return_stats else stats[0]))
+
+
+def rms_norm(x, weight=None, eps=1e-6, *, shift=None, scale=None, want_factor=False):
+    """RMSNorm over the last dimension, optional weight, optional AdaLN modulation with shift/scale of shape
+    [batch, hidden] (x is [batch, tokens, hidden]). Returns y or (y, factor)."""
+    if torch.is_grad_enabled() and x.requires_grad:
+        raise RuntimeError('Fused RMSNorm requires inference mode')
+    _check_bf16(x, weight, shift, scale)
+    hidden = x.shape[-1]
+    if weight is not None and weight.numel() != hidden:
+        raise ValueError('Fused RMSNorm supports BF16 inputs matching the weight')
+    if (shift is None) != (scale is None):
+        raise ValueError('shift and scale come together')
+    rows = x.numel() // hidden
+    per_batch = rows
+    if shift is not None:
+        if shift.shape != scale.shape or shift.shape[-1] != hidden or rows % (shift.numel() // hidden):
+            raise ValueError('shift/scale must be [batch, hidden] with batch dividing the rows of x')
+        per_batch = rows // (shift.numel() // hidden)
+    require_sm100(x.device)
+    y = torch.empty_like(x)
+    stats, scratch = _stats(x.device, want_factor)
+    _lib.check(_lib.load().tw_rms_norm(_ptr(x), _ptr(weight), _ptr(shift), _ptr(scale), _ptr(y), _ptr(stats), _ptr(scratch),
+                                       rows, hidden, per_batch, float(eps), _stream(x.device)))
+    return (y, stats[0]) if want_factor else y
+
+
+def rms_norm_heads(x, eps=1e-6):
+    """RMSNorm over head_dim = 128 of a (possibly strided) view [..., tokens, heads, 128] whose leading
+    dimensions fold into the token stride; returns a contiguous tensor of the same shape."""
+    if x.dtype != torch.bfloat16 or not x.is_cuda or x.shape[-1] != 128 or x.stride(-1) != 1:
+        raise ValueError('expected a CUDA BF16 view [..., heads, 128] with unit inner stride')
+    require_sm100(x.device)
+    heads = x.shape[-2]
+    lead = x.reshape(-1, heads, 128) if x.dim() != 3 else x       # a view when the leading dims are foldable
+    if lead.data_ptr() != x.data_ptr():
+        raise ValueError('leading dimensions must fold into one token stride')
+    y = torch.empty(x.shape, device=x.device, dtype=x.dtype)
+    _lib.check(_lib.load().tw_rms_norm_heads(_ptr(lead), _ptr(y), lead.shape[0], heads, lead.stride(0), lead.stride(1),
+                                             float(eps), _stream(x.device)))
+    return y
+
+
+def gate_residual_(x, gate, y):
+    """x += gate[:, None, :] * y in place; x, y [batch, tokens, hidden], gate [batch, hidden]."""
+    _check_bf16(x, gate, y)
+    hidden = x.shape[-1]
+    rows = x.numel() // hidden
+    if y.shape != x.shape or gate.shape[-1] != hidden or rows % (gate.numel() // hidden):
+        raise ValueError('shapes do not match')
+    require_sm100(x.device)
+    _lib.check(_lib.load().tw_gate_residual(_ptr(x), _ptr(gate), _ptr(y), rows, hidden, rows // (gate.numel() // hidden),
+                                            _stream(x.device)))
+    return x

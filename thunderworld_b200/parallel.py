@@ -121,3 +121,11 @@ def global_factor(x_local, topo):
     if topo.tp_size > 1:
         dist.all_reduce(peak, op=dist.ReduceOp.MAX, group=topo.tp_group)
     return torch.where(peak > 0, peak / 2688., torch.ones_like(peak)).reshape(())
+
+
+def global_factor_from_peak(peak, topo):
+    """Same, starting from the shard's max|x| (1-element float32 tensor, overwritten) that the producer of x
+    already reduced."""
+    if topo.tp_size > 1:
+        dist.all_reduce(peak, op=dist.ReduceOp.MAX, group=topo.tp_group)
+    return torch.where(peak > 0, peak / 2688., torch.ones_like(peak)).reshape(())
