@@ -366,8 +366,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (threadIdx.x == 0) {
     tw::mbar_init(qFull, 1);
     for (int i = 0; i < ATT_SLOTS; ++i) {
-      tw::mbar_init(kFull + i, 1); tw::mbar_init(kEmpty + i, 5);   // MMA commit + the 4 softmax warps of the tile's group (kf)
-      tw::mbar_init(vFull + i, 1); tw::mbar_init(vEmpty + i, 9);   // MMA commit + 8 accumulate warps (vf)
+      tw::mbar_init(kFull + i, 1); tw::mbar_init(kEmpty + i, 4);   // the 4 softmax warps of the tile's group, after S and kf are consumed
+      tw::mbar_init(vFull + i, 1); tw::mbar_init(vEmpty + i, 8);   // the 8 accumulate warps, after T and vf are consumed
     }
     for (int i = 0; i < 2; ++i) {
       tw::mbar_init(sFull + i, 1); tw::mbar_init(sEmpty + i, 4);
@@ -468,36 +468,40 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (p.terms == 4) mma(TM_S + par * 128, L::OFF_Q + ATT_TILE, k1, TM_SFQ1, TM_SFK1 + par * 8, false);
           }
         }
-        tw::tc_commit(sFull + par);
-        tw::tc_commit(kEmpty + s);
+        tw::tc_commit(sFull + par);        // (the K slot is released by the softmax group once it has read kf)
         return true;
       };
+      // S is double-buffered by tile parity = by softmax group. The scores of tile t + 2 are issued as soon as
+      // the group of tile t has pulled S[t & 1] into registers (sEmpty), which is well before it posts P(t):
+      // its next scores are ready when it comes back, instead of queueing behind the P V product.
       if (ok) ok = issue_qk(0);
+      if (ok && p.nt > 1) ok = issue_qk(1);
       for (int t = 0; t < p.nt && ok; ++t) {
-        if (t + 1 < p.nt) ok = issue_qk(t + 1);
+        if (t + 2 < p.nt) ok = issue_qk(t + 2);
         if (!ok) break;
         const uint32_t s = t % ATT_SLOTS, ph = (t / ATT_SLOTS) & 1, par = t & 1;
-        ok = tw::mbar_wait(pFull + par, (t >> 1) & 1, abort_flag) && tw::mbar_wait(vFull + s, ph, abort_flag) &&
-             tw::mbar_wait(tEmpty, (t & 1) ^ 1, abort_flag);
-        if (!ok) break;
-        tw::tc_fence_after();
         const bool rep = sel[t] & 2;
         const int p0 = L::OFF_P + par * 2 * ATT_TILE, p1 = p0 + ATT_TILE;
         const int v0 = L::OFF_V + s * 2 * ATT_TILE, v1 = v0 + ATT_TILE;
-        copy_sf(TM_SFP0 + par * 8, L::OFF_SFP + par * 2 * ATT_SF);
+        // the V scale factors do not depend on P: copy them while the softmax group is still writing it
+        ok = tw::mbar_wait(vFull + s, ph, abort_flag);
+        if (!ok) break;
         copy_sf(TM_SFV0 + par * 8, L::OFF_SFV + s * 2 * ATT_SF);
+        if (rep && p.pv_terms >= 3) copy_sf(TM_SFV1 + par * 8, L::OFF_SFV + (s * 2 + 1) * ATT_SF);
+        ok = tw::mbar_wait(pFull + par, (t >> 1) & 1, abort_flag) && tw::mbar_wait(tEmpty, (t & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        tw::tc_fence_after();
+        copy_sf(TM_SFP0 + par * 8, L::OFF_SFP + par * 2 * ATT_SF);
         mma(TM_T, p0, v0, TM_SFP0 + par * 8, TM_SFV0 + par * 8, true);
         if (rep) {
           copy_sf(TM_SFP1 + par * 8, L::OFF_SFP + (par * 2 + 1) * ATT_SF);
           mma(TM_T, p1, v0, TM_SFP1 + par * 8, TM_SFV0 + par * 8, false);
           if (p.pv_terms >= 3) {
-            copy_sf(TM_SFV1 + par * 8, L::OFF_SFV + (s * 2 + 1) * ATT_SF);
             mma(TM_T, p0, v1, TM_SFP0 + par * 8, TM_SFV1 + par * 8, false);
             if (p.pv_terms == 4) mma(TM_T, p1, v1, TM_SFP1 + par * 8, TM_SFV1 + par * 8, false);
           }
         }
-        tw::tc_commit(tFull);
-        tw::tc_commit(vEmpty + s);
+        tw::tc_commit(tFull);              // (the V slot is released by the accumulate warps once they have read vf)
         tw::tc_commit(pEmpty + par);
       }
     }
