@@ -37,26 +37,41 @@ __device__ __forceinline__ float load_factor(const PackParams& p) {
   return peak > 0.f ? __fdiv_rn(peak, 2688.f) : 1.f;
 }
 
-// max |bf16(x * d)| over the tensor, as the bit pattern of a non-negative float.
+// max |bf16(x * d)| over the tensor, as the bit pattern of a non-negative float. Each thread keeps four
+// 16-byte loads in flight; without a prescale the maximum is taken on packed bf16 pairs (the maximum of
+// bf16 magnitudes is a bf16 value, so nothing is rounded).
 template <bool PRESCALE>
 __global__ void __launch_bounds__(256) amax_kernel(const uint4* __restrict__ x, const float* __restrict__ d,
                                                    long long vecs, int k, unsigned* __restrict__ out) {
   float peak = 0.f;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < vecs;
-       i += (long long)gridDim.x * blockDim.x) {
-    uint4 v = __ldg(x + i);
-    uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    int col = (int)((i * 8) % k);
+  __nv_bfloat162 pk = __floats2bfloat162_rn(0.f, 0.f);
+  for (long long base = (long long)blockIdx.x * 1024; base < vecs; base += (long long)gridDim.x * 1024) {
+    uint4 v[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      float lo = tw::bf16_bits_to_float(w[j] & 0xffffu), hi = tw::bf16_bits_to_float(w[j] >> 16);
+      const long long i = base + j * 256 + threadIdx.x;
+      v[j] = i < vecs ? __ldg(x + i) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
       if (PRESCALE) {
-        lo = __bfloat162float(__float2bfloat16_rn(__fmul_rn(lo, __ldg(d + col + 2 * j))));
-        hi = __bfloat162float(__float2bfloat16_rn(__fmul_rn(hi, __ldg(d + col + 2 * j + 1))));
+        const long long i = base + j * 256 + threadIdx.x;
+        const int col = (int)((i * 8) % k);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float lo = tw::bf16_bits_to_float(w[q] & 0xffffu), hi = tw::bf16_bits_to_float(w[q] >> 16);
+          lo = __bfloat162float(__float2bfloat16_rn(__fmul_rn(lo, __ldg(d + col + 2 * q))));
+          hi = __bfloat162float(__float2bfloat16_rn(__fmul_rn(hi, __ldg(d + col + 2 * q + 1))));
+          peak = fmaxf(peak, fmaxf(fabsf(lo), fabsf(hi)));
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) pk = __hmax2(pk, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[q])));
       }
-      peak = fmaxf(peak, fmaxf(fabsf(lo), fabsf(hi)));
     }
   }
+  if (!PRESCALE) peak = fmaxf(__low2float(pk), __high2float(pk));
 #pragma unroll
   for (int o = 16; o; o >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, o));
   if ((threadIdx.x & 31) == 0 && peak > 0.f) atomicMax(out, __float_as_uint(peak));
@@ -303,7 +318,7 @@ extern "C" int tw_quantize(const TwQuantizeArgs* a, void* stream_) {
   if (!a->factor_given) {
     if (cudaMemsetAsync(amax, 0, sizeof(unsigned), stream) != cudaSuccess) return TW_ERR_LAUNCH;
     long long vecs = (long long)a->m * a->k / 8;
-    int blocks = (int)((vecs + 255) / 256 < 148 * 8 ? (vecs + 255) / 256 : 148 * 8);
+    int blocks = (int)((vecs + 1023) / 1024 < 148 * 8 ? (vecs + 1023) / 1024 : 148 * 8);
     if (a->prescale)
       amax_kernel<true><<<blocks, 256, 0, stream>>>(static_cast<const uint4*>(a->x), a->prescale, vecs, a->k, amax);
     else
