@@ -88,6 +88,21 @@ __device__ __forceinline__ float div_by(float a, float b, float r) {
   float q = __fmaf_rn(e, r, q0);
   return __uint_as_float(__float_as_uint(q) | (__float_as_uint(a) & 0x80000000u));
 }
+// Two quotients per instruction (fma.rn.f32x2 of sm_100): same three-operation sequence, without the
+// sign fix; `nb` = -b. Callers restore the sign of zero where it is observable (the E2M1 code of -0).
+__device__ __forceinline__ float2 div_by2(float2 a, float nb, float r) {
+  const float2 r2 = make_float2(r, r);
+  const float2 q0 = __fmul2_rn(a, r2);
+  const float2 e = __ffma2_rn(make_float2(nb, nb), q0, a);
+  return __ffma2_rn(e, r2, q0);
+}
+__device__ __forceinline__ float with_sign_of(float q, float a) {
+  return __uint_as_float(__float_as_uint(q) | (__float_as_uint(a) & 0x80000000u));
+}
+// four code bytes (one per register, upper bits clear) -> one word, first byte lowest
+__device__ __forceinline__ uint32_t pack4(uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) {
+  return __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
+}
 // The two values of one code byte (low nibble first) as floats, exact.
 __device__ __forceinline__ float2 e2m1x2_values(uint32_t byte) {
   uint32_t h2;
@@ -122,6 +137,31 @@ __device__ __forceinline__ uint32_t scale_offset(int row, int col, int cols) {
          (uint32_t)((row & 127) >> 5) * 4u + (uint32_t)(col & 3);
 }
 
+// Same for eight value pairs. `sign` (optional) supplies the sign of zero quotients: sign[i] has the sign
+// the i-th pair's codes must carry (the pre-division values, whose -0 the packed division lost).
+template <bool FAST, bool SIGN>
+__device__ __forceinline__ uint32_t encode_group2(const float2 (&z)[8], const float2 (&sign)[8], float multiplier,
+                                                  uint32_t (&bytes)[8], float& scale_value) {
+  float peak = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) peak = fmaxf(peak, fmaxf(fabsf(z[i].x), fabsf(z[i].y)));
+  float raw = __fdiv_rn(__fmul_rn(peak, multiplier), 6.f);
+  raw = fminf(fmaxf(raw, 0.001953125f), 448.f);
+  const uint32_t sb = tw::f32_to_e4m3(raw);
+  const float s = tw::e4m3_to_f32(sb);
+  const float rs = __frcp_rn(s);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float2 q;
+    if (FAST) q = div_by2(z[i], -s, rs);
+    else q = make_float2(__fdiv_rn(z[i].x, s), __fdiv_rn(z[i].y, s));
+    if (SIGN) { q.x = with_sign_of(q.x, sign[i].x); q.y = with_sign_of(q.y, sign[i].y); }
+    bytes[i] = tw::f32x2_to_e2m1x2(q.x, q.y);
+  }
+  scale_value = s;
+  return sb;
+}
+
 // grid (K/128, ceil(M/128)); each CTA packs one 128x128 tile of the lattice.
 template <bool PRESCALE, int REPAIR>
 __global__ void __launch_bounds__(PACK_THREADS, 4) pack_kernel(PackParams p) {
@@ -151,7 +191,7 @@ __global__ void __launch_bounds__(PACK_THREADS, 4) pack_kernel(PackParams p) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) sens[i] = __ldg(p.sensitivity + col + i);
   }
-  float score = 0.f;
+  float2 score2 = make_float2(0.f, 0.f);
   // all four passes' loads are issued before any arithmetic so that 128 bytes per thread are in flight
   uint4 raw[4][2];
 #pragma unroll
@@ -184,30 +224,35 @@ __global__ void __launch_bounds__(PACK_THREADS, 4) pack_kernel(PackParams p) {
         for (int i = 0; i < 16; ++i) y[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(y[i], dsc[i])));
       }
     }
-    float z[16];
+    // z = y / f, two per instruction; the sign of a zero is carried by y
+    float2 y2[8], z2[8];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) z[i] = FAST ? div_by(y[i], f, rf) : __fdiv_rn(y[i], f);
+    for (int i = 0; i < 8; ++i) {
+      y2[i] = make_float2(y[2 * i], y[2 * i + 1]);
+      z2[i] = FAST ? div_by2(y2[i], -f, rf) : make_float2(__fdiv_rn(y[2 * i], f), __fdiv_rn(y[2 * i + 1], f));
+    }
     uint2 c0, c1 = make_uint2(0u, 0u);
     float s0, s1;
-    uint32_t sb0 = encode_group(z, p.base, c0, s0), sb1 = 0u;
+    uint32_t b0[8];
+    uint32_t sb0 = encode_group2<FAST, true>(z2, y2, p.base, b0, s0), sb1 = 0u;
+    c0 = make_uint2(pack4(b0[0], b0[1], b0[2], b0[3]), pack4(b0[4], b0[5], b0[6], b0[7]));
     if (planes2) {
-      float r[16];
-      const uint32_t w[2] = {c0.x, c0.y};
+      float2 r2[8];
+      const float2 ns0 = make_float2(-s0, -s0);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float2 val = e2m1x2_values((w[i >> 2] >> (8 * (i & 3))) & 0xffu);
         // the product value * scale is exact in float32, so one FMA equals multiply-then-subtract
-        r[2 * i] = __fmaf_rn(-val.x, s0, z[2 * i]);
-        r[2 * i + 1] = __fmaf_rn(-val.y, s0, z[2 * i + 1]);
+        r2[i] = __ffma2_rn(e2m1x2_values(b0[i]), ns0, z2[i]);
         if (REPAIR == 3) {
           // selector energy in the normalised domain: sum r^2 * sens (the common factor f^2 of the
           // unnormalised residual does not change the ranking or the energy-prefix ratio)
-          score = __fmaf_rn(__fmul_rn(r[2 * i], r[2 * i]), sens[2 * i], score);
-          score = __fmaf_rn(__fmul_rn(r[2 * i + 1], r[2 * i + 1]), sens[2 * i + 1], score);
+          score2 = __ffma2_rn(__fmul2_rn(r2[i], r2[i]), make_float2(sens[2 * i], sens[2 * i + 1]), score2);
         }
       }
       if (active) {
-        sb1 = encode_group(r, p.res, c1, s1);
+        uint32_t b1[8];
+        sb1 = encode_group2<FAST, false>(r2, r2, p.res, b1, s1);
+        c1 = make_uint2(pack4(b1[0], b1[1], b1[2], b1[3]), pack4(b1[4], b1[5], b1[6], b1[7]));
         if (p.gain != 1.f) sb1 = tw::f32_to_e4m3(fminf(__fmul_rn(s1, p.gain), 448.f));
       }
     }
@@ -239,6 +284,7 @@ __global__ void __launch_bounds__(PACK_THREADS, 4) pack_kernel(PackParams p) {
   };
   if (fast) run(std::true_type{}); else run(std::false_type{});
   if (REPAIR == 3) {
+    float score = __fadd_rn(score2.x, score2.y);
 #pragma unroll
     for (int o = 16; o; o >>= 1) score = __fadd_rn(score, __shfl_xor_sync(0xffffffffu, score, o));
     if ((t & 31) == 0) warp_scores[t >> 5] = score;
