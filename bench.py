@@ -27,9 +27,10 @@ sys.path.insert(0, ROOT)
 M_TOKENS = 7680
 PROJECTIONS = (('qkv', 6144, 2048), ('out', 2048, 2048), ('ffn_up', 8192, 2048), ('ffn_down', 2048, 8192))
 NOMINAL_FP4_TFLOPS = 9000.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one fused_kernel<256> launch (qkv, 2x plan), from the
-# ncu capture summarised under profiles/; None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of the four fused_kernel<256> launches of one step (M = 7680,
+# 2x plan), from the one-pass full-size ncu capture summarised under profiles/ (bytes per launch, by layer).
+NCU_TRAFFIC_BY_LAYER = {'qkv': 71.1e6, 'out': 18.9e6, 'ffn_up': 103.6e6, 'ffn_down': 81.7e6}
+NCU_TRAFFIC_BYTES_PER_LAUNCH = sum(NCU_TRAFFIC_BY_LAYER.values()) / len(NCU_TRAFFIC_BY_LAYER)
 
 
 def plan_for(name, n, k, budget, seed):
@@ -477,7 +478,10 @@ def main():
                          'frac': achieved / NOMINAL_FP4_TFLOPS,
                          'peak_source': 'nominal dense FP4 (MEASURED_PEAKS.json holds no FP4 figure)',
                          'frac_of_4x_measured_bf16': achieved / (4 * peaks['bf16_tflops_sustained']) if peaks else None,
-                         'traffic': NCU_TRAFFIC_BYTES_PER_LAUNCH, 'launches': gemm_launches,
+                         'traffic': (NCU_TRAFFIC_BYTES_PER_LAUNCH if args.m_tokens == M_TOKENS and args.budget == 2.0 and
+                                     args.layers == 'qkv,out,ffn_up,ffn_down' else None),
+                         'traffic_unit': 'bytes per launch (ncu dram read + write, mean of the four layers)',
+                         'launches': gemm_launches,
                          'avg_launch_ms': gemm_ms / gemm_launches,
                          'per_layer_tflops': {n_: flops_by_layer[n_] / (np.mean(v) * 1e-3) / 1e12 for n_, v in per_layer.items()},
                          'gemm_share_of_step': gemm_ms / ms},

@@ -120,3 +120,25 @@ def test_explicit_mask_batch_and_graph_engine():
         fp4_attention(q[..., :64], k, v)
     with pytest.raises(ValueError):
         fp4_attention(q.float(), k, v)
+
+
+@pytest.mark.parametrize('n_keys', [3840, 512])
+@pytest.mark.parametrize('coverage,terms', [(0., 3), (.5, 3)])
+def test_full_size_softmax_weights_sum_to_one(n_keys, coverage, terms):
+    """Size-independent property at the benchmark's shape (batch 2 x 32 heads x 3840 queries, self and
+    512-key cross): with V constant along the keys the output must equal that constant per channel,
+    whatever Q and K are - every row's probabilities, their on-chip FP4 re-quantization (base and residual
+    planes) and the denominator have to agree. V = const is exactly representable (one value per scale
+    group), so the only error is the E2M1 rounding of P, which averages out over the keys."""
+    from thunderworld_b200 import RepairConfig, fp4_attention
+    g = torch.Generator().manual_seed(n_keys)
+    scale = (torch.rand(32, generator=g) * 1.5 + .5)[None, None, :, None]
+    q = (torch.randn((2, 3840, 32, 128), generator=g) * scale).bfloat16().cuda()
+    k = (torch.randn((2, n_keys, 32, 128), generator=g) * scale).bfloat16().cuda()
+    channel = (torch.randn(128, generator=g) * 2).bfloat16()
+    v = channel[None, None, None, :].expand(2, n_keys, 32, 128).contiguous().cuda()
+    out = fp4_attention(q, k, v, RepairConfig(coverage=coverage, terms=terms)).float().cpu()
+    want = channel.float()[None, None, None, :].expand_as(out)
+    rel = float((out - want).norm() / want.norm())
+    assert rel < 0.03, rel
+    assert torch.isfinite(out).all()
