@@ -268,9 +268,15 @@ def run_step(args):
                                                  f'{args.tokens} tokens x CFG 2, {args.budget}x plan, CUDA Graph replay',
                                      'parallelism': f'tp{topo.tp_size} x cfg{cfg_par}'},
                           'issued_tflop_per_step': issued / 1e12, 'effective_tflops': issued / 1e12 / (float(t[0]) * 1e-3),
-                          'ledger_ratio': None if ledger is None else ledger['ratio']}))
+                          'ledger_ratio': None if ledger is None else ledger['ratio']}), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # The captured graphs hold NCCL kernels: tearing the communicator down while they exist can block
+        # for ever, so the graphs go first and the process leaves without destroying the group.
+        engine.graphs.clear()
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def run_attention(args):

@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(128) select_kernel(SelectParams p) {
 //   T = P0 V0 [+ P1 V0 + P0 V1 + P1 V1]                                          tcgen05, fp32 in TMEM
 //   acc = acc * alpha + T * pf[m] * vf[d]
 // Warps: 0 producer (TMA + bulk copies), 1 MMA issuer (scale copies smem -> TMEM, MMAs, commits),
-// 4..11 softmax / accumulate (row = TMEM lane, two warps per lane quadrant). No cluster, no multicast.
+// 4..11 softmax (two groups of four warps), 12..19 accumulate (row = TMEM lane). No cluster, no multicast.
 namespace {
 
 constexpr int ATT_TILE = 128 * 64;        // bytes of a 128 x 128 NVFP4 code tile
