@@ -203,19 +203,42 @@ __global__ void __launch_bounds__(128) select_kernel(SelectParams p) {
   float* score = sim + 8 * p.nt * 8;      // [nt]
   const int h = blockIdx.x, mt = blockIdx.y, kh = h / (p.hq / p.hk), t = threadIdx.x;
   const int samples = p.nt * 8;
-  for (int i = t; i < 8 * 128; i += 128) {
-    const int row = min(mt * 128 + (i >> 7) * 16, p.m - 1);
-    qs[i] = __bfloat162float(p.q[(size_t)row * p.q_row + (size_t)h * p.q_head + (i & 127)]);
+  {                                         // eight sampled query rows: thread t loads 8 channels of row t / 16
+    const int i = t >> 4, c = t & 15;
+    const int row = min(mt * 128 + i * 16, p.m - 1);
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p.q + (size_t)row * p.q_row + (size_t)h * p.q_head) + c);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      qs[i * 128 + c * 8 + 2 * j] = tw::bf16_bits_to_float(w[j] & 0xffffu);
+      qs[i * 128 + c * 8 + 2 * j + 1] = tw::bf16_bits_to_float(w[j] >> 16);
+    }
   }
   __syncthreads();
   for (int s = t; s < samples; s += 128) {
     const int key = (s >> 3) * 128 + (s & 7) * 16;
-    const __nv_bfloat16* kp = p.k + (size_t)min(key, p.n - 1) * p.k_row + (size_t)kh * p.k_head;
+    // one key row = 256 contiguous bytes: sixteen 16-byte loads; the products are accumulated in channel order
+    const uint4* kp = reinterpret_cast<const uint4*>(p.k + (size_t)min(key, p.n - 1) * p.k_row + (size_t)kh * p.k_head);
     float acc[8] = {};
-    for (int d = 0; d < 128; ++d) {
-      const float kv = __bfloat162float(kp[d]);
+#pragma unroll 2
+    for (int c = 0; c < 16; ++c) {
+      const uint4 raw = __ldg(kp + c);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+      float kv[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = __fmaf_rn(qs[i * 128 + d], kv, acc[i]);
+      for (int j = 0; j < 4; ++j) {
+        kv[2 * j] = tw::bf16_bits_to_float(w[j] & 0xffffu);
+        kv[2 * j + 1] = tw::bf16_bits_to_float(w[j] >> 16);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 qa = *reinterpret_cast<const float4*>(qs + i * 128 + c * 8);
+        const float4 qb = *reinterpret_cast<const float4*>(qs + i * 128 + c * 8 + 4);
+        float a = acc[i];
+        a = __fmaf_rn(qa.x, kv[0], a); a = __fmaf_rn(qa.y, kv[1], a); a = __fmaf_rn(qa.z, kv[2], a); a = __fmaf_rn(qa.w, kv[3], a);
+        a = __fmaf_rn(qb.x, kv[4], a); a = __fmaf_rn(qb.y, kv[5], a); a = __fmaf_rn(qb.z, kv[6], a); a = __fmaf_rn(qb.w, kv[7], a);
+        acc[i] = a;
+      }
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) sim[i * samples + s] = key < p.n ? acc[i] * 0.08838834764831845f : -INFINITY;
@@ -800,6 +823,8 @@ extern "C" int tw_select_tiles(const TwSelectArgs* a, void* stream_) {
   if (!a || !a->q || !a->k || !a->energy || !a->flags || !a->counts) return TW_ERR_ARGUMENT;
   if (a->m <= 0 || a->n <= 0 || a->hq <= 0 || a->hk <= 0 || a->hq % a->hk) return TW_ERR_ARGUMENT;
   if (a->pvflags && !a->pvcounts) return TW_ERR_ARGUMENT;
+  if ((((uintptr_t)a->q | (uintptr_t)a->k) & 15) || ((a->q_stride_row | a->q_stride_head | a->k_stride_row | a->k_stride_head) & 7))
+    return TW_ERR_ALIGNMENT;                                // 16-byte row loads
   SelectParams p{};
   p.q = static_cast<const __nv_bfloat16*>(a->q); p.k = static_cast<const __nv_bfloat16*>(a->k);
   p.energy = a->energy; p.flags = a->flags; p.pvflags = a->pvflags; p.counts = a->counts; p.pvcounts = a->pvcounts;
