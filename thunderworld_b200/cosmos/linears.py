@@ -122,16 +122,17 @@ class RepairLinear(torch.nn.Module):
         identity = bool(self.asset.get('identity_prescale', False))
         if packed is None:
             common = dict(wg=op.wg, base=base, res=res)
+            d = None if identity else op.d               # an identity prescale is bf16(x * 1) = x: skip the multiply
             if self.asset.get('selector') == 'residual_sensitivity' and 0 < op.na < kb:
                 # online current-residual selection: mask written in place, then read by the GEMM
-                packed = ops.quantize(x, op.d, repair=3, na=op.na, sensitivity=self.sensitivity, mask=op.am,
+                packed = ops.quantize(x, d, repair=3, na=op.na, sensitivity=self.sensitivity, mask=op.am,
                                       factor=factor if identity else None, energy=self.repair_energy, **common)
             else:
                 if 0 < op.na < kb:                       # sampled-energy selector of assets without sensitivities
                     op.am.copy_(sampled_block_rank(x, op.d, m, k) < op.na)
                 mode = 0 if op.na == 0 else (1 if op.na == kb else 2)
                 use_factor = factor if (base, res) == (1., 1.) else None
-                packed = ops.quantize(x, op.d, repair=mode, mask=op.am if mode == 2 else None, factor=use_factor, **common)
+                packed = ops.quantize(x, d, repair=mode, mask=op.am if mode == 2 else None, factor=use_factor, **common)
         y = op.run_packed(x, packed)
         return y if self.bias is None else y + self.bias
 

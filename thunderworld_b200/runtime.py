@@ -136,6 +136,16 @@ def _forward_one(q, k, v, config, repair_mask, counts_tensor, return_mask, out):
     return selected, keepalive
 
 
+_side_streams = {}
+
+
+def _side_stream(device, index):
+    key = (device, index)
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device)
+    return _side_streams[key]
+
+
 def _forward(q, k, v, config, repair_mask=None, counts_tensor=None, return_mask=False):
     _validate(q, k, v)
     if not isinstance(config, RepairConfig):
@@ -143,11 +153,29 @@ def _forward(q, k, v, config, repair_mask=None, counts_tensor=None, return_mask=
     batch = q.shape[0]
     out = torch.empty(tuple(q.shape), device=q.device, dtype=q.dtype)
     masks, keep = [], []
+    # Batch entries are independent problems (CFG cond / uncond). Entry 0 runs on the caller's stream, the
+    # others on side streams that fork from it and join it again, so that the tail of one entry's
+    # attention grid (960 CTAs = 6.5 waves of 148) is filled by the next entry's CTAs. The fork / join is
+    # made of events only, which a CUDA Graph capture of the caller's stream records as parallel branches.
+    main = torch.cuda.current_stream(q.device)
+    fork = None
+    if batch > 1:
+        fork = torch.cuda.Event()
+        fork.record(main)
     for b in range(batch):
         mask_b = None
         if repair_mask is not None:
             mask_b = repair_mask if batch == 1 and repair_mask.ndim == 3 else repair_mask[b]
-        selected, held = _forward_one(q[b], k[b], v[b], config, mask_b, counts_tensor, return_mask, out[b])
+        if b == 0:
+            selected, held = _forward_one(q[b], k[b], v[b], config, mask_b, counts_tensor, return_mask, out[b])
+        else:
+            side = _side_stream(q.device, b)
+            side.wait_event(fork)
+            with torch.cuda.stream(side):
+                selected, held = _forward_one(q[b], k[b], v[b], config, mask_b, counts_tensor, return_mask, out[b])
+                join = torch.cuda.Event()
+                join.record(side)
+            main.wait_event(join)
         masks.append(selected)
         keep.append(held)
     selected = None
