@@ -101,7 +101,8 @@ typedef struct TwRepairIO {
   int32_t mask_per_n;      /* nonzero: mask is bool [ceil(m/128), n/128, k/128], one A support per output
                               block (explicit masks of FP4Linear, thunderworld_fp4/linear.py:115-119) */
 } TwRepairIO;
-/* Bytes of caller-owned workspace (holds the device status word; zero it once). */
+/* Limits: n % 128 == 0, k % 128 == 0, k <= 24576 (else the "size exceeds the stated maximum" status).
+ * Bytes of caller-owned workspace (holds the device status word; zero it once). */
 size_t tw_workspace(int m, int n, int k);
 int tw_fused(int m, int n, int k, const void* a_codes, const void* w_codes, const void* sfa_swz,
              const void* sfb_swz, void* out_bf16, const float* alpha_dev, void* workspace, void* stream,

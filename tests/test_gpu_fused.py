@@ -61,6 +61,7 @@ CASES = [
     (384, 768, 1024, 0.5, 0.5, True),       # four terms with cross, 128-wide tiles
     (512, 1024, 2048, 0.25, 0.25, True),
     (256, 256, 256, 1.0, 1.0, True),        # dense W1 addressing
+    (130, 256, 24576, 0.25, 0.25, False),   # the largest supported K (192 blocks: the Super-shaped FFN-down)
 ]
 
 

@@ -2,6 +2,10 @@
 // TMA (cp.async.bulk[.tensor]) and tcgen05 (tensor memory + block-scaled MMA)
 // wrappers written as inline PTX. No multicast forms are used anywhere.
 #pragma once
+// Isolation switches (never defined in the shipped build; the build script only forwards extra nvcc flags
+// given in its environment): TW_EXP_NOLOAD, TW_EXP_NOMMA, TW_EXP_NOCP, TW_EXP_CPONLY, TW_EXP_ARRIVE,
+// TW_EXP_TESTWAIT, TW_EXP_NOFENCE and TW_EXP_NOSTORE compile one class of operations out of the kernels so
+// that the cost of that class can be measured; results of such builds are wrong by construction.
 #include <cstdint>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>

@@ -26,7 +26,7 @@
 
 namespace {
 
-constexpr int KB_MAX = 128;               // K <= 16384
+constexpr int KB_MAX = 192;               // K <= 24576
 constexpr int UNIT_TILE = 128 * 64;       // bytes of one 128-row x K128 code tile
 constexpr int SF_ATOM = 1024;             // bytes of the scales of 128 rows x K128
 
