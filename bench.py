@@ -426,21 +426,54 @@ def main():
     if ops.device_status(device) != 0:
         raise RuntimeError('device status word reports a bounded-wait timeout')
 
-    # end to end: pinned host inputs in, outputs back to pinned host memory, every step
+    # end to end: pinned host inputs in, outputs back to pinned host memory, every step. The copies run on
+    # their own streams (PCIe is full duplex): a layer's upload overlaps the previous layer's quantizer + GEMM
+    # and the download of the layer before that. Each layer keeps one device input and one device output, so
+    # its upload waits for its previous use to be computed and its compute waits for its previous output to
+    # be downloaded.
+    g_layer = {}
+    for layer in layers:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            layer.quantize(layer.x)
+            layer.gemm(layer.x)
+        g_layer[layer.name] = g
+    up, down = torch.cuda.Stream(), torch.cuda.Stream()
+    uploaded = {layer.name: torch.cuda.Event() for layer in layers}
+    computed = {layer.name: torch.cuda.Event() for layer in layers}
+    downloaded = {layer.name: torch.cuda.Event() for layer in layers}
+    for layer in layers:
+        computed[layer.name].record(stream)
+        downloaded[layer.name].record(stream)
+
     def step_e2e():
         for layer in layers:
-            layer.x.copy_(layer.x_host, non_blocking=True)
-        g_step.replay()
+            up.wait_event(computed[layer.name])
+            with torch.cuda.stream(up):
+                layer.x.copy_(layer.x_host, non_blocking=True)
+                uploaded[layer.name].record(up)
+            stream.wait_event(uploaded[layer.name])
+            stream.wait_event(downloaded[layer.name])
+            g_layer[layer.name].replay()
+            computed[layer.name].record(stream)
+            down.wait_event(computed[layer.name])
+            with torch.cuda.stream(down):
+                layer.out_host.copy_(layer.out, non_blocking=True)
+                downloaded[layer.name].record(down)
+
+    def drain_e2e():
         for layer in layers:
-            layer.out_host.copy_(layer.out, non_blocking=True)
+            stream.wait_event(downloaded[layer.name])
 
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for _ in range(0 if args.no_e2e else 2):
         step_e2e()
+    drain_e2e()
     barrier()
     s0.record(stream)
     for _ in range(0 if args.no_e2e else args.steps):
         step_e2e()
+    drain_e2e()
     s1.record(stream)
     barrier()
     ms_e2e = max(s0.elapsed_time(s1), 1e-9)

@@ -59,6 +59,10 @@ def _worker(rank, world, port, results):
         assert torch.allclose(torch.cat(gathered, 1), x @ w.T, atol=1e-4)
         zero = parallel.global_factor(torch.zeros(4, 128), topo)
         assert float(zero) == 1.0
+        # the same factor from the shard's own max|x| (what a fused producer hands over)
+        peak = xs.abs().amax().float().reshape(1)
+        assert torch.equal(parallel.global_factor_from_peak(peak, topo), factor)
+        assert float(parallel.global_factor_from_peak(torch.zeros(1), topo)) == 1.0
         results[rank] = 1
     finally:
         dist.destroy_process_group()
