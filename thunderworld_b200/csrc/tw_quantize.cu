@@ -164,7 +164,7 @@ __device__ __forceinline__ uint32_t encode_group2(const float2 (&z)[8], const fl
 
 // grid (K/128, ceil(M/128)); each CTA packs one 128x128 tile of the lattice.
 template <bool PRESCALE, int REPAIR>
-__global__ void __launch_bounds__(PACK_THREADS, 4) pack_kernel(PackParams p) {
+__global__ void __launch_bounds__(PACK_THREADS, 3) pack_kernel(PackParams p) {
   __shared__ float warp_scores[PACK_THREADS / 32];
   const int kb = blockIdx.x, mbi = blockIdx.y;
   const int t = threadIdx.x, cg = t & 7, r0 = t >> 3;
