@@ -4,7 +4,7 @@
 #pragma once
 // Isolation switches (never defined in the shipped build; the build script only forwards extra nvcc flags
 // given in its environment): TW_EXP_NOLOAD, TW_EXP_NOMMA, TW_EXP_NOCP, TW_EXP_CPONLY, TW_EXP_ARRIVE,
-// TW_EXP_TESTWAIT, TW_EXP_NOFENCE and TW_EXP_NOSTORE compile one class of operations out of the kernels so
+// TW_EXP_TESTWAIT and TW_EXP_NOSTORE compile one class of operations out of the kernels so
 // that the cost of that class can be measured; results of such builds are wrong by construction.
 #include <cstdint>
 #include <cuda_runtime.h>
@@ -55,13 +55,6 @@ __device__ __forceinline__ uint32_t f32x2_to_e2m1x2(float lo, float hi) {
   asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %2, %1; cvt.u32.u8 %0, t; }" : "=r"(r) : "f"(lo), "f"(hi));
   return r;
 }
-// Value of a 4-bit E2M1 code.
-__device__ __forceinline__ float e2m1_value(uint32_t code) {
-  uint32_t mag = code & 7u;
-  float v = mag < 4u ? 0.5f * (float)mag : (mag < 6u ? (float)mag - 2.f : 2.f * (float)mag - 8.f);
-  return (code & 8u) ? -v : v;
-}
-
 // ---------------------------------------------------------------------------
 // Shared-memory addresses, mbarriers
 // ---------------------------------------------------------------------------
@@ -135,13 +128,6 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, v
   return ok != 0;
 }
 
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{ .reg .b32 r; .reg .pred p; elect.sync r|p, 0xffffffff; selp.u32 %0, 1, 0, p; }" : "=r"(pred));
-  return pred != 0;
-}
-
 // ---------------------------------------------------------------------------
 // TMA
 // ---------------------------------------------------------------------------
@@ -173,17 +159,6 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
       "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
       ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void tma_store_2d(const void* tmap, const void* src, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-               ::"l"(tmap), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void bulk_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-template <int N> __device__ __forceinline__ void bulk_wait_all() {
-  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
-}
 
 // ---------------------------------------------------------------------------
 // tcgen05: tensor memory and block-scaled MMA (cta_group::1 only)
@@ -200,13 +175,6 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t columns) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-// Mainloop variant: the operands were written by the async proxy (TMA) and are read by the async
-// proxy (tcgen05), ordered by the mbarrier itself.
-__device__ __forceinline__ void tc_fence_after_load() {
-#ifndef TW_EXP_NOFENCE
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#endif
-}
 // Arrives once on `bar` when every tcgen05 operation issued so far by this thread has completed.
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
 #ifdef TW_EXP_ARRIVE
