@@ -76,10 +76,9 @@ def _cfg_worker(rank, world, port, results):
         assert (topo.tp_rank, topo.cfg_rank) == (0, rank)
         # each CFG rank computes one branch; guidance combines them with one exchange
         branch = torch.full((4,), float(rank + 1))
-        both = [torch.empty(4) for _ in range(2)]
-        dist.all_gather(both, branch, group=topo.cfg_group)
-        guided = both[1] + 3.0 * (both[0] - both[1])
+        guided = parallel.guide(branch, 3.0, topo)
         assert torch.equal(guided, torch.full((4,), 2 + 3.0 * (1 - 2)))
+        assert parallel.guide(branch, 3.0, parallel.Topology()) is branch
         results[rank] = 1
     finally:
         dist.destroy_process_group()

@@ -129,3 +129,16 @@ def global_factor_from_peak(peak, topo):
     if topo.tp_size > 1:
         dist.all_reduce(peak, op=dist.ReduceOp.MAX, group=topo.tp_group)
     return torch.where(peak > 0, peak / 2688., torch.ones_like(peak)).reshape(())
+
+
+def guide(branch_output, scale, topo):
+    """Classifier-free guidance across the CFG split: CFG rank 0 holds the conditional output, rank 1 the
+    unconditional one; every rank gets  uncond + scale * (cond - uncond)  after one all-gather of
+    [tokens, hidden] over its CFG group (ranks of the same tensor-parallel index)."""
+    if topo.cfg_size == 1:
+        return branch_output
+    if topo.cfg_size != 2:
+        raise ValueError('guidance combines exactly two branches')
+    both = [torch.empty_like(branch_output) for _ in range(2)]
+    dist.all_gather(both, branch_output.contiguous(), group=topo.cfg_group)
+    return both[1] + scale * (both[0] - both[1])
