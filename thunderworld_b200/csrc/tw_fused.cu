@@ -30,11 +30,14 @@ constexpr int KB_MAX = 192;               // K <= 24576
 constexpr int UNIT_TILE = 128 * 64;       // bytes of one 128-row x K128 code tile
 constexpr int SF_ATOM = 1024;             // bytes of the scales of 128 rows x K128
 
-template <int BN> struct Cfg {
+// DEEP = true trades one base stage for deeper repair-unit rings: at the 2x plan a K256 step takes long
+// enough for two base stages, and the issuer waits less for unit scales; without repair terms the third
+// base stage is worth 16 %. The host picks the variant from the plan.
+template <int BN, bool DEEP = false> struct Cfg {
   static constexpr int HALVES = BN / 128;
-  static constexpr int STAGES = BN == 256 ? 3 : 4;            // base stages (K256 of A0 and W0)
-  static constexpr int A1_SLOTS = 3;                          // A1 units
-  static constexpr int W1_SLOTS = 3;                          // W1 units
+  static constexpr int STAGES = BN == 256 ? (DEEP ? 2 : 3) : 4;   // base stages (K256 of A0 and W0)
+  static constexpr int A1_SLOTS = DEEP && BN == 256 ? 4 : 3;      // A1 units
+  static constexpr int W1_SLOTS = DEEP && BN == 256 ? 6 : 3;      // W1 units
   static constexpr int TAB_SLOTS = 3;                         // per-tile term tables built ahead
   static constexpr int ACC_STAGES = BN == 256 ? 1 : 2;
   static constexpr int EPI_WARPS = 8;
@@ -68,7 +71,8 @@ template <int BN> struct Cfg {
   static constexpr int TM_COLS = 512;
   static_assert(A1_SLOTS * 8 <= 32 && TM_SFW1 + 8 * W1_SLOTS <= TM_COLS, "tensor memory budget");
 };
-static_assert(Cfg<256>::SMEM_BYTES <= 232448 && Cfg<128>::SMEM_BYTES <= 232448, "shared memory budget");
+static_assert(Cfg<256>::SMEM_BYTES <= 232448 && Cfg<256, true>::SMEM_BYTES <= 232448 && Cfg<128>::SMEM_BYTES <= 232448,
+              "shared memory budget");
 
 struct Params {
   const uint8_t* sfa0;      // atom-layout scales of A0  [MB*128, K/16]
@@ -133,11 +137,11 @@ __device__ __forceinline__ void build_table(TermTable<BN>& tab, const Params& p,
   __syncwarp();
 }
 
-template <int BN>
-__global__ void __launch_bounds__(Cfg<BN>::THREADS, 1)
+template <int BN, bool DEEP>
+__global__ void __launch_bounds__(Cfg<BN, DEEP>::THREADS, 1)
 fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
              const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1, const Params p) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, DEEP>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
@@ -545,10 +549,10 @@ bool make_map(CUtensorMap* map, int rank, const void* base, const cuuint64_t* di
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN>
+template <int BN, bool DEEP>
 int launch(int m, int n, int k, const void* a_codes, const void* w_codes, const void* sfa, const void* sfb, void* out,
            const float* alpha, void* workspace, cudaStream_t stream, const TwRepairIO* io, int sms) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, DEEP>;
   CUtensorMap tm_a0, tm_a1, tm_w0, tm_w1;
   const int planes = io->na > 0 ? 2 : 1;
   {
@@ -590,12 +594,12 @@ int launch(int m, int n, int k, const void* a_codes, const void* w_codes, const 
   p.tiles = p.mb * p.tiles_n;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(fused_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(fused_kernel<BN, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
       return TW_ERR_LAUNCH;
     configured = true;
   }
   const int grid = p.tiles < sms ? p.tiles : sms;
-  fused_kernel<BN><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tm_a0, tm_a1, tm_w0, tm_w1, p);
+  fused_kernel<BN, DEEP><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tm_a0, tm_a1, tm_w0, tm_w1, p);
   return cudaGetLastError() == cudaSuccess ? TW_OK : TW_ERR_LAUNCH;
 }
 
@@ -631,6 +635,11 @@ extern "C" int tw_fused(int m, int n, int k, const void* a_codes, const void* w_
   cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
   if (major != 10) return TW_ERR_ARCH;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (n % 256 == 0 && !io->mask_per_n) return launch<256>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms);
-  return launch<128>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms);
+  if (n % 256 == 0 && !io->mask_per_n) {
+    // with W1 tiles and an A1 quota of at least half the K blocks the unit rings are the scarcer resource
+    // (2x plan: +1 %), below that the third base stage is (1.5x plan: +1.3 %, base plan: +16 %)
+    if (io->hasw && 2 * io->na >= k / 128) return launch<256, true>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms);
+    return launch<256, false>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms);
+  }
+  return launch<128, false>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms);
 }
