@@ -200,3 +200,19 @@ def test_tree_signature_clone_copy():
     assert trees.signature({'x': torch.zeros(2, 3)}) != trees.signature({'x': torch.zeros(3, 2)})
     with pytest.raises(TypeError):
         trees.signature(object())
+
+
+def test_cfg_parallel_rank_compiles_its_own_branch():
+    """A CFG-parallel rank runs branch 1 of the plan as its only branch: its rows carry the plan's branch
+    index, the ledger it proves counts one branch."""
+    from thunderworld_b200.cosmos.engine import StepEngine
+    from thunderworld_b200.cosmos.settings import RunConfig
+    engine = StepEngine(RunConfig(compute_budget=2.), branches=1)
+    engine._branch_offset = 1
+    for ph in range(4):
+        row = linear_cost(256, 256, 512, a_blocks=2, w_blocks=(0, 3))
+        engine.rows[('linear', 'proj', 1, ph)] = {**row, 'name': 'proj', 'branch': 1, 'phase': ph}
+        att = attention_cost(256, 256, 2, 2, qk_counts=[1, 1], pv_counts=[1, 1])
+        engine.rows[('attention', '0', 1, ph)] = {**att, 'name': '0', 'branch': 1, 'phase': ph}
+    ledger = engine.compile_budget()
+    assert ledger['feasible'] and ledger['total_mma'] <= 2 * ledger['base_mma']

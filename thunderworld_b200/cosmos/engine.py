@@ -110,7 +110,9 @@ class StepEngine:
             raise ValueError('no compute budget configured')
         modules = sorted({name for kind, name, _, _ in self.rows if kind == 'linear'})
         layers = sorted({name for kind, name, _, _ in self.rows if kind == 'attention'})
-        return compile_request(list(self.rows.values()), self.config.compute_budget, steps=self.steps,
+        # a CFG-parallel rank runs one fixed branch of the plan: its ledger counts that branch as its only one
+        rows = [{**row, 'branch': row['branch'] - self._branch_offset} for row in self.rows.values()]
+        return compile_request(rows, self.config.compute_budget, steps=self.steps,
                                branches=self.branches, expected_modules=modules, expected_layers=layers)
 
     def warm_schedule(self, model, **kwargs):
