@@ -49,7 +49,10 @@ class PackedRows:
         blocks = ops.cdiv(rows_padded, 128)
         self.codes = torch.empty((planes, heads * rows_padded, 64), device=dev, dtype=torch.uint8)
         self.scales = torch.empty((planes, heads * rows_padded, 8), device=dev, dtype=torch.float8_e4m3fn)
-        self.scales_swz = torch.zeros((planes, heads, blocks, 1024), device=dev, dtype=torch.uint8)
+        # every byte of an atom is written by the packer for rows below rows_padded: padding atoms exist only
+        # when rows_padded is not a multiple of 128, and only then the buffer has to start zeroed
+        make = torch.zeros if rows_padded % 128 else torch.empty
+        self.scales_swz = make((planes, heads, blocks, 1024), device=dev, dtype=torch.uint8)
         self.factors = torch.empty((heads * rows_padded,), device=dev, dtype=torch.float32)
         self.energy = torch.empty((heads, blocks, 8), device=dev, dtype=torch.float32) if need_energy else None
         args = _lib.PackRowsArgs(x.data_ptr(), self.codes.data_ptr(), self.scales.data_ptr(), self.scales_swz.data_ptr(),
