@@ -62,6 +62,7 @@ CASES = [
     (512, 1024, 2048, 0.25, 0.25, True),
     (256, 256, 256, 1.0, 1.0, True),        # dense W1 addressing
     (130, 256, 24576, 0.25, 0.25, False),   # the largest supported K (192 blocks: the Super-shaped FFN-down)
+    (9600, 512, 256, 0.5, 0.5, False),      # 150 tiles on 148 SMs: two rounds of the persistent schedule
 ]
 
 
