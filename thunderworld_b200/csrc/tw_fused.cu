@@ -15,7 +15,7 @@
 // CTA = one 128 x BN output tile at a time (persistent over tiles), warp-specialised:
 //   warp 0      producer of base stages (TMA, 128-byte swizzle; bulk copies of scale atoms)
 //   warp 1      MMA issuer: MMAs, scale copies of repair units, commits
-//   warp 2      producer of repair units (TMA, 64-byte swizzle)
+//   warps 2, 6  producers of repair units (A1 blocks / W1 tiles; TMA, 64-byte swizzle)
 //   warp 3      builds the per-tile term tables (A-support bits, W1 bank positions) ahead of use
 //   warps 4,5   copy the base-stage scale atoms smem -> TMEM (tcgen05.cp) ahead of the MMA issuer
 //   warps 8-15  epilogue: TMEM -> registers -> bf16 -> global (32-byte stores)
@@ -171,7 +171,7 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
     for (int i = 0; i < C::STAGES; ++i) { tw::mbar_init(fullS + i, 1); tw::mbar_init(emptyS + i, 1); }
     for (int i = 0; i < C::A1_SLOTS; ++i) { tw::mbar_init(fullA1 + i, 1); tw::mbar_init(emptyA1 + i, 1); }
     for (int i = 0; i < C::W1_SLOTS; ++i) { tw::mbar_init(fullW1 + i, 1); tw::mbar_init(emptyW1 + i, 1); }
-    for (int i = 0; i < C::TAB_SLOTS; ++i) { tw::mbar_init(tabFull + i, 1); tw::mbar_init(tabEmpty + i, 2 + C::SF_THREADS); }
+    for (int i = 0; i < C::TAB_SLOTS; ++i) { tw::mbar_init(tabFull + i, 1); tw::mbar_init(tabEmpty + i, 3 + C::SF_THREADS); }
     for (int i = 0; i < C::ACC_STAGES; ++i) { tw::mbar_init(accFull + i, 1); tw::mbar_init(accEmpty + i, C::EPI_WARPS); }
     for (int i = 0; i < C::STAGES; ++i) tw::mbar_init(sfFull + i, C::SF_THREADS);
     for (int i = 0; i < C::A1_SLOTS; ++i) tw::mbar_init(usfA + i, 1);
@@ -221,10 +221,12 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
         }
       }
     }
-  } else if (warp == 2) {
-    // ------------------------------------------------------------------ producer of repair units
-    // Per step, in the order the MMA issuer consumes them: A1(kb0), A1(kb1), then W1 tiles by (kb, half).
+  } else if (warp == 2 || warp == 6) {
+    // ------------------------------------------------------------------ producers of repair units
+    // Per step, in the order the MMA issuer consumes them: A1(kb0), A1(kb1) by warp 2, W1 tiles by
+    // (kb, half) by warp 6: a full W1 ring does not hold the A1 loads of the next step back.
     if (lane == 0) {
+      const bool do_a = warp == 2, do_w = warp == 6;
       uint32_t ia = 0, iw = 0, it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
@@ -241,7 +243,7 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
           }
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
-            if (!((abits >> j) & 1u) || !ok) continue;
+            if (!do_a || !((abits >> j) & 1u) || !ok) continue;
             const uint32_t s = ia % C::A1_SLOTS, ph = (ia / C::A1_SLOTS) & 1; ++ia;
             ok = tw::mbar_wait(emptyA1 + s, ph ^ 1, abort_flag);
             if (!ok) continue;
@@ -253,7 +255,7 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
           for (int j = 0; j < 2; ++j) {
 #pragma unroll
             for (int h = 0; h < C::HALVES; ++h) {
-              if (!((wbits[h] >> j) & 1u) || !ok) continue;
+              if (!do_w || !((wbits[h] >> j) & 1u) || !ok) continue;
               const int loc = tab.w1loc[h][kb0 + j];
               const uint32_t s = iw % C::W1_SLOTS, ph = (iw / C::W1_SLOTS) & 1; ++iw;
               ok = tw::mbar_wait(emptyW1 + s, ph ^ 1, abort_flag);
