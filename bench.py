@@ -72,6 +72,7 @@ class Layer:
         self.x = self.x_host.to(device, non_blocking=True)
         w = (torch.randn(n, k, generator=gen) * 0.02).bfloat16().to(device)
         wc, ws, wg = quantize_weight(w)
+        self.weights = (wc, ws, wg)                                               # both planes, for the parity check
         am = torch.zeros(mb, kb, dtype=torch.bool); am[:, :self.na] = True       # placeholder support, rewritten online
         wm = torch.zeros(nb * kb, dtype=torch.bool); wm[self.tiles] = True
         self.op = Native(wc, ws, wg, torch.ones(k, device=device), am.repeat_interleave(128, 1).to(device),
@@ -101,6 +102,43 @@ class Layer:
         support = [row.nonzero().flatten().tolist() for row in self.op.am.cpu()]
         return linear_cost(self.m, self.n, self.k, a_blocks=self.na, w_blocks=self.tiles, cross=self.cross,
                            a_support=support)['total_mma']
+
+
+def layer_parity(layer, blocks):
+    """Checks one projection of the timed workload against the CPU oracle on the given M128 row blocks, at full
+    N and K (output rows are independent given the packed bytes, so a few blocks cost seconds on the host):
+    the quantizer's bytes of those rows (bit-exact, given the tensor factor the GPU reduced over all rows), the
+    selector's realised support of those blocks (equal to the oracle's ranking except blocks whose score lies
+    within float32 rounding of the cut) and the fused GEMM output (relative L2 against the decoded fp32
+    emulation fed with the GPU's own bytes and realised mask). Returns a dict; raises nothing."""
+    import torch
+    from oracle import nvfp4_oracle as o
+    u8 = lambda t: (t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t).cpu().numpy()
+    op, pk = layer.op, layer.packed
+    kb = layer.k // 128
+    rows = torch.cat([torch.arange(b * 128, min((b + 1) * 128, layer.m)) for b in blocks]).to(layer.x.device)
+    codes, scales = u8(pk.codes[:, rows]), u8(pk.scales[:, rows])
+    factor = pk.factor.item()
+    x_rows = layer.x[rows].float().cpu().numpy()
+    oc, osb, _ = o.quantize_linear_input(x_rows, factor=factor, rows_padded=len(rows))
+    bytes_equal = bool(np.array_equal(oc[:codes.shape[0]], codes) and np.array_equal(osb[:scales.shape[0]], scales))
+    mask = None
+    mask_ok = True
+    if layer.na:
+        mask = op.am[torch.as_tensor(blocks, device=op.am.device)].cpu().numpy()
+        scores, _ = o.residual_scores(x_rows, None, layer.sens.cpu().numpy(), factor=factor)
+        want = o.choose_blocks(scores, layer.na)
+        for i in range(len(blocks)):
+            diff = np.flatnonzero(mask[i] != want[i])
+            cut = np.sort(scores[i])[-layer.na]
+            mask_ok &= bool(mask[i].sum() == layer.na and np.all(np.abs(scores[i][diff] - cut) <= 1e-4 * cut))
+    wc, ws, wg = layer.weights
+    want = o.repair_linear(codes, scales, factor, u8(wc), u8(ws), wg.item(), len(rows), a_mask=mask,
+                           a_full=layer.na == kb, w_tiles=layer.tiles, cross=layer.cross)
+    got = layer.out[rows].float().cpu().numpy()
+    rel = float(np.linalg.norm(got.astype(np.float64) - want) / max(np.linalg.norm(want), 1e-30))
+    return {'layer': layer.name, 'rows': int(len(rows)), 'rel_l2': rel, 'packed_bytes_bit_exact': bytes_equal,
+            'selector_matches_oracle': bool(mask_ok), 'finite': bool(np.isfinite(got).all())}
 
 
 class ClockSampler(threading.Thread):
@@ -174,7 +212,7 @@ def run_reference(args):
 
 
 def workload_config(budget, world, m=M_TOKENS, layers='qkv,out,ffn_up,ffn_down'):
-    return {'workload': f'cosmos3-edge projection set (config 1), M={m}, layers {layers}, '
+    return {'workload': f'cosmos3-edge projection set, M={m}, layers {layers}, '
                         f'{budget}x issued-work plan, cross term on FFN-down',
             'budget': budget, 'replicas': world, 'parallelism': f'dp{world}',
             'l2': 'per-step working set ~0.55 GB (activations, packed planes, outputs) exceeds the 126 MB L2'}
@@ -201,7 +239,7 @@ def step_plan(cfg, budget, seed=0):
 
 
 def run_step(args):
-    """DiT denoise-step time (BASELINE configs 3 and 4): one graph replay of the whole step, CFG batch 2
+    """DiT denoise-step time (Nano- and Super-shaped synthetic DiT): one graph replay of the whole step, CFG batch 2
     (split over GPU pairs when --cfg-parallel 2), tensor parallel over the remaining ranks."""
     import torch
     import torch.distributed as dist
@@ -280,7 +318,7 @@ def run_step(args):
 
 
 def run_attention(args):
-    """Streaming FP4 attention (BASELINE config 2): batch 2 (CFG) x heads x seq x 128, self- and
+    """Streaming FP4 attention workload: batch 2 (CFG) x heads x seq x 128, self- and
     cross-attention (512 text keys), base and 50 % / 3-term repair; time includes packing and selection."""
     import torch
     from thunderworld_b200 import RepairConfig
@@ -318,7 +356,7 @@ def run_attention(args):
                       'unit': 'TFLOP/s', 'n_gpus': 1, 'steps': args.steps, 'warmup': max(args.warmup, 3),
                       'ms_per_step': best['ms'], 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
                       'dtype': 'nvfp4 (e2m1 x ue4m3, fp32 softmax)', 'data': 'synthetic',
-                      'config': {'workload': f'attention config 2: batch 2 x {H} heads x seq {S} x 128, cross 512 keys'},
+                      'config': {'workload': f'streaming attention: batch 2 x {H} heads x seq {S} x 128, cross 512 keys'},
                       'cases': results,
                       'roofline': {'bound': 'tensor', 'achieved': best['tflops'], 'peak': NOMINAL_FP4_TFLOPS, 'unit': 'TFLOP/s',
                                    'frac': best['tflops'] / NOMINAL_FP4_TFLOPS, 'traffic': None}}))
@@ -332,6 +370,7 @@ def main():
     ap.add_argument('--impl', default='ours')
     ap.add_argument('--budget', type=float, default=2.0)
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-parity', action='store_true', help='skip the oracle check of the outputs (profiling runs)')
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer timing (profiling runs)')
     ap.add_argument('--m-tokens', type=int, default=M_TOKENS, help='rows per projection (smaller for profiler captures)')
     ap.add_argument('--layers', default='qkv,out,ffn_up,ffn_down', help='subset of the projection set')
@@ -425,6 +464,18 @@ def main():
     sampler.stop_flag = True
     if ops.device_status(device) != 0:
         raise RuntimeError('device status word reports a bounded-wait timeout')
+    # outputs of the timed workload against the CPU oracle (after the timed region; rank 0 only)
+    parity = None
+    if rank == 0 and not args.no_parity:
+        g_step.replay()
+        torch.cuda.synchronize()
+        mb = (args.m_tokens + 127) // 128
+        checks = [layer_parity(layer, sorted({0, mb - 1})) for layer in layers]
+        parity = {'rel_l2': max(c['rel_l2'] for c in checks), 'rows': sum(c['rows'] for c in checks),
+                  'tolerance': 1e-3, 'packed_bytes_bit_exact': all(c['packed_bytes_bit_exact'] for c in checks),
+                  'selector_matches_oracle': all(c['selector_matches_oracle'] for c in checks),
+                  'against': 'CPU oracle (decoded fp32 emulation), first and last M128 row block of every layer at full N and K',
+                  'layers': checks}
 
     # end to end: pinned host inputs in, outputs back to pinned host memory, every step. The copies run on
     # their own streams (PCIe is full duplex): a layer's upload overlaps the previous layer's quantizer + GEMM
@@ -511,6 +562,7 @@ def main():
             'e2e': {'value': e2e, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
                     'ms_per_step': ms_e2e / args.steps},
             'gpu_launches': args.steps * len(layers) * 4,
+            'parity': parity,
             'clocks': sampler.result(),
             'roofline': {'bound': 'tensor', 'kernel': 'fused_kernel (tcgen05 mxf4nvf4 repair GEMM)',
                          'achieved': achieved, 'peak': NOMINAL_FP4_TFLOPS, 'unit': 'TFLOP/s',

@@ -82,7 +82,7 @@ def test_fused_matches_oracle(m, n, k, af, wf, cross):
 
 
 def test_config0_full_size_and_deterministic():
-    """BASELINE config 0: M=3840, K=N=2048, full A1, 64 of 256 W1 tiles."""
+    """The single repaired linear layer workload: M=3840, K=N=2048, full A1, 64 of 256 W1 tiles."""
     op, x, weights, am, tiles = build(3840, 2048, 2048, 0, 1.0, 0.25, False)
     assert len(tiles) == 64
     packed = op.pack(x)
@@ -92,6 +92,27 @@ def test_config0_full_size_and_deterministic():
     assert torch.equal(y1, y2)
     want = oracle_output(op, x, weights, packed, am, tiles, False)
     assert rel_l2(y1.float().cpu().numpy(), want) <= TOL
+
+
+@pytest.mark.parametrize('budget', [2.0, 1.5])
+@pytest.mark.parametrize('index', [0, 1, 2, 3])
+def test_projection_set_layers_at_benchmark_shape(index, budget):
+    """The four projections the benchmark times (M = 7680; QKV 6144x2048, out 2048x2048, FFN-up 8192x2048,
+    FFN-down 2048x8192 with the cross term), built exactly as the benchmark builds them: online A1 selection
+    (repair mode 3) writes the support the GEMM reads in the same stream. Checked against the oracle on the
+    first, middle and last M128 row block at full N and K; tolerance 1e-3 on the output, bytes bit-exact."""
+    import bench
+    from thunderworld_b200 import ops
+    name, n, k = bench.PROJECTIONS[index]
+    layer = bench.Layer(name, n, k, bench.M_TOKENS, budget, index, torch.device('cuda', 0))
+    layer.quantize(layer.x)
+    layer.gemm(layer.x)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    mb = bench.M_TOKENS // 128
+    res = bench.layer_parity(layer, [0, mb // 2, mb - 1])
+    assert res['packed_bytes_bit_exact'] and res['selector_matches_oracle'] and res['finite'], res
+    assert res['rel_l2'] <= TOL, res
 
 
 def test_linearity_in_alpha_and_zero_activation():

@@ -102,3 +102,36 @@ def test_issued_flops_matches_ledger_formula():
     f = o.issued_flops(m, n, k, a_full=True, w_tiles=tiles)
     assert f == 2 * m * n * k * 2 + 2 * m * 128 * 128 * 64
     assert abs(f / 1e9 - 72.5) < 0.1
+
+
+def _bf16(bits):
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+@pytest.mark.parametrize('case', ['base', 'repair3', 'repair4_pv2'])
+def test_attention_flow_matches_reference_run(golden_dir, case):
+    """oracle.attention_reference against outputs of the reference's tests/oracle.py:reference, run on CPU with
+    its own quant_ref decode (splits 1 and 2, 2/3/4 terms, separate PV flags, GQA, ragged M and N).
+    Both are float32 flows over identical quantized operands; they differ in the summation order of the
+    float32 matmuls and of the split merge, and a P value on a rounding boundary can take the other code."""
+    g = load(golden_dir, 'attention_flow.npz')[case]
+    got = o.attention_reference(_bf16(g['q_bf16']), _bf16(g['k_bf16']), _bf16(g['v_bf16']), g['flags'],
+                                repair=bool(g['repair']), terms=int(g['terms']), pvflags=g['pvflags'],
+                                pvterms=int(g['pvterms']))
+    want = g['out']
+    assert got.shape == want.shape
+    rel = np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want)
+    assert rel < 2e-4, rel
+
+
+@pytest.mark.parametrize('case', ['m129', 'm416', 'wide'])
+def test_selector_matches_reference_loop(golden_dir, case):
+    """oracle.residual_scores + choose_blocks against the stable-argsort selector loop of the reference's own
+    test (tests/test_adaptive_repair.py:52-63) evaluated on the reference's CPU encoder, with and without the
+    energy-prefix stop."""
+    g = load(golden_dir, 'selector.npz')[case]
+    x = _bf16(g['x_bf16'])
+    scores, _ = o.residual_scores(x, g['d'], g['sens'], base=0.875)
+    assert np.allclose(scores, g['scores'], rtol=2e-5, atol=0)
+    for energy, key in ((0.5, 'mask_050'), (0.75, 'mask_075'), (1.0, 'mask_100')):
+        assert np.array_equal(o.choose_blocks(scores, int(g['count']), energy), g[key]), energy

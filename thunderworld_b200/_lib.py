@@ -70,6 +70,10 @@ def load():
     meta = json.loads(META_PATH.read_text())
     if meta.get('library_sha256') != _sha(LIB_PATH):
         raise RuntimeError('libtwb200.so does not match its build record; rebuild it')
+    from . import build as _build
+    if meta.get('sources_sha256') != _build.source_hash():
+        raise RuntimeError('libtwb200.so was built from other sources than the ones beside it; rebuild it '
+                           '(`python -m thunderworld_b200.build`)')
     lib = ctypes.CDLL(str(LIB_PATH))
     lib.tw_status.argtypes = [_i]; lib.tw_status.restype = ctypes.c_char_p
     lib.tw_abi_version.argtypes = []; lib.tw_abi_version.restype = _i

@@ -7,7 +7,6 @@ source and binary hashes that the loader re-checks.
 """
 import hashlib
 import json
-import os
 import shutil
 import subprocess
 from pathlib import Path
@@ -40,14 +39,13 @@ def nvcc_path():
 
 def build(force=False, verbose=False):
     """Compile when sources changed (or `force`). Returns the library path."""
-    want = source_hash() + os.environ.get('TWB200_NVCC_FLAGS', '')
+    want = source_hash()
     if not force and LIB.exists() and META.exists():
         meta = json.loads(META.read_text())
         if meta.get('sources_sha256') == want and meta.get('library_sha256') == _sha([LIB]):
             return LIB
     srcs = [str(CSRC / s) for s in SOURCES if (CSRC / s).exists()]
-    extra = os.environ.get('TWB200_NVCC_FLAGS', '').split()      # experiment switches (-DTW_EXP_...)
-    cmd = [nvcc_path(), *FLAGS, *extra, '-o', str(LIB), *srcs, '-lcuda']
+    cmd = [nvcc_path(), *FLAGS, '-o', str(LIB), *srcs, '-lcuda']
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or proc.returncode:
         print(proc.stdout, proc.stderr)

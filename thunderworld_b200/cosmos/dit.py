@@ -36,8 +36,8 @@ class DiTConfig:
             raise ValueError('hidden and ffn must be multiples of 128')
 
 
-NANO = DiTConfig(4096, 32, 16384, 28)      # Cosmos3-Nano-shaped step (BASELINE config 3)
-SUPER = DiTConfig(6144, 48, 24576, 48)     # Cosmos3-Super-shaped step (BASELINE config 4)
+NANO = DiTConfig(4096, 32, 16384, 28)      # Cosmos3-Nano-shaped step: 28 blocks, hidden 4096, 32 heads, FFN 16384
+SUPER = DiTConfig(6144, 48, 24576, 48)     # Cosmos3-Super-shaped step: 48 blocks, hidden 6144, 48 heads, FFN 24576
 
 
 class _Source:

@@ -4,9 +4,9 @@
 //   pack_qk :12-25, pack_v :29-47, streaming_attention :51-124, select_tiles_head :191-215
 // and the per-row-factor quantizer _quantize.py:7-39 (factor = max(|row|max / 1536, 1e-12)).
 // Packing is redone for every call; nothing about old inputs is cached. P is quantized on chip.
-#include <cstdio>
 #include <type_traits>
 #include <cuda.h>
+#include <atomic>
 #include "tw_common.cuh"
 #include "../../include/twb200.h"
 
@@ -148,7 +148,6 @@ __global__ void __launch_bounds__(256) pack_v_kernel(RowPackParams p) {
   }
   __syncthreads();
   const int lane8 = t & 7;
-  float esum = 0.f;
 #pragma unroll 1
   for (int pass = 0; pass < 4; ++pass) {
     const int d = pass * 32 + (t >> 3);
@@ -164,7 +163,6 @@ __global__ void __launch_bounds__(256) pack_v_kernel(RowPackParams p) {
       for (int o = 1; o < 32; o <<= 1) e += __shfl_xor_sync(0xffffffffu, e, o);
       // a warp covers 4 channels; 4 warps (16 channels) form one group of the 8 per tile
       if ((t & 31) == 0) energy_part[pass * 2 + ((t >> 5) >> 2)][(t >> 5) & 3] = e;
-      (void)esum;
     }
     quantize_row_group(p, x, head, nt * 128 + d, lane8, true);
   }
@@ -852,9 +850,13 @@ extern "C" int tw_attention(const TwAttentionArgs* a, void* stream_) {
   if (nt > ATT_NT_MAX) return TW_ERR_TOO_LARGE;
   if (a->repair && !a->full && !a->flags) return TW_ERR_ARGUMENT;
   if (a->pv_repair && !a->pv_full && !a->pvflags) return TW_ERR_ARGUMENT;
+  // TMA bases and bulk copies need 16-byte alignment; the output rows are written with 32-byte stores
+  const uintptr_t align16 = (uintptr_t)a->qc | (uintptr_t)a->kc | (uintptr_t)a->vc | (uintptr_t)a->sfq | (uintptr_t)a->sfk |
+                            (uintptr_t)a->sfv | (uintptr_t)a->qf | (uintptr_t)a->kf | (uintptr_t)a->vf;
+  if ((align16 & 15) || ((uintptr_t)a->out & 31)) return TW_ERR_ALIGNMENT;
   if (!att_encode_fn()) return TW_ERR_DRIVER;
   int dev = 0, major = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return TW_ERR_LAUNCH;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TW_ERR_LAUNCH;
   cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
   if (major != 10) return TW_ERR_ARCH;
   const int q_planes = a->repair ? 2 : 1;
@@ -871,14 +873,15 @@ extern "C" int tw_attention(const TwAttentionArgs* a, void* stream_) {
   p.m = a->m; p.n = a->n; p.hq = a->hq; p.hk = a->hk; p.mp = a->mp; p.np = a->np; p.mblk = mblk; p.nt = nt;
   p.repair = a->repair; p.full = a->full; p.terms = a->terms;
   p.pv_repair = a->pv_repair; p.pv_full = a->pv_full; p.pv_terms = a->pv_terms;
-  static bool configured = false;
-  if (!configured) {
+  // the shared-memory opt-in is a per-device attribute of the function
+  static std::atomic<bool> configured[64];
+  if (!configured[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttSmem::BYTES) != cudaSuccess)
       return TW_ERR_LAUNCH;
     // the in-kernel register rebalance assumes the launch allocation it was sized for
     cudaFuncAttributes attr;
     if (cudaFuncGetAttributes(&attr, attention_kernel) != cudaSuccess || attr.numRegs < ATT_REGS_LAUNCH) return TW_ERR_LAUNCH;
-    configured = true;
+    configured[dev].store(true, std::memory_order_release);
   }
   attention_kernel<<<dim3((a->m + 127) / 128, a->hq), ATT_THREADS, AttSmem::BYTES, static_cast<cudaStream_t>(stream_)>>>(tm_q, tm_k, tm_v, p);
   return cudaGetLastError() == cudaSuccess ? TW_OK : TW_ERR_LAUNCH;

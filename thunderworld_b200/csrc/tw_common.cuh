@@ -2,10 +2,6 @@
 // TMA (cp.async.bulk[.tensor]) and tcgen05 (tensor memory + block-scaled MMA)
 // wrappers written as inline PTX. No multicast forms are used anywhere.
 #pragma once
-// Isolation switches (never defined in the shipped build; the build script only forwards extra nvcc flags
-// given in its environment): TW_EXP_NOLOAD, TW_EXP_NOMMA, TW_EXP_NOCP, TW_EXP_CPONLY, TW_EXP_ARRIVE,
-// TW_EXP_TESTWAIT and TW_EXP_NOSTORE compile one class of operations out of the kernels so
-// that the cost of that class can be measured; results of such builds are wrong by construction.
 #include <cstdint>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
@@ -66,10 +62,6 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-#ifdef TW_EXP_NOLOAD
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-  return;
-#endif
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -77,12 +69,6 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
-#ifdef TW_EXP_TESTWAIT
-  asm volatile(
-      "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-#endif
   asm volatile(
       "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
@@ -135,26 +121,17 @@ __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const void* tmap, int x, int y, uint64_t* bar) {
-#ifdef TW_EXP_NOLOAD
-  return;
-#endif
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_u32(dst)), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void tma_load_3d(void* dst, const void* tmap, int x, int y, int z, uint64_t* bar) {
-#ifdef TW_EXP_NOLOAD
-  return;
-#endif
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
       ::"r"(smem_u32(dst)), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
 }
 // Untiled bulk copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-#ifdef TW_EXP_NOLOAD
-  return;
-#endif
   asm volatile(
       "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
       ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
@@ -177,26 +154,16 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 // Arrives once on `bar` when every tcgen05 operation issued so far by this thread has completed.
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
-#ifdef TW_EXP_ARRIVE
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-  return;
-#endif
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                ::"r"(smem_u32(bar)) : "memory");
 }
 // 32 rows x 16 bytes of shared memory -> 4 TMEM columns, replicated to the four lane quadrants.
 __device__ __forceinline__ void tc_copy_scales(uint32_t tmem_addr, uint64_t smem_desc) {
-#if defined(TW_EXP_NOMMA) || defined(TW_EXP_NOCP)
-  return;
-#endif
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(smem_desc) : "memory");
 }
 // D[tmem] (+)= A[smem] * B[smem]^T, E2M1 operands with one UE4M3 scale per 16 elements of K; K = 64.
 __device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
-#if defined(TW_EXP_NOMMA) || defined(TW_EXP_CPONLY)
-  return;
-#endif
   asm volatile(
       "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
       "  tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p; }"

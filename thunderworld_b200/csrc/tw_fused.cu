@@ -20,6 +20,7 @@
 //   warps 4,5   copy the base-stage scale atoms smem -> TMEM (tcgen05.cp) ahead of the MMA issuer
 //   warps 8-15  epilogue: TMEM -> registers -> bf16 -> global (32-byte stores)
 // No cluster, no multicast.
+#include <atomic>
 #include <cuda.h>
 #include "tw_common.cuh"
 #include "../../include/twb200.h"
@@ -473,11 +474,7 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
       const int row = mbi * 128 + quad * 32 + lane;
       const int col = nt * BN + group * C::EPI_COLS;
       __nv_bfloat16* dst = p.out + (size_t)row * p.n + col;
-#ifdef TW_EXP_NOSTORE
-      const bool store = row < 0;
-#else
       const bool store = row < p.m && col < p.n;
-#endif
       // 64 columns per round: two back-to-back TMEM loads, one wait; the TMEM stage is handed back
       // after the last round's loads, before that round is converted and stored
 #pragma unroll
@@ -553,7 +550,7 @@ bool make_map(CUtensorMap* map, int rank, const void* base, const cuuint64_t* di
 
 template <int BN, bool DEEP>
 int launch(int m, int n, int k, const void* a_codes, const void* w_codes, const void* sfa, const void* sfb, void* out,
-           const float* alpha, void* workspace, cudaStream_t stream, const TwRepairIO* io, int sms) {
+           const float* alpha, void* workspace, cudaStream_t stream, const TwRepairIO* io, int sms, int dev) {
   using C = Cfg<BN, DEEP>;
   CUtensorMap tm_a0, tm_a1, tm_w0, tm_w1;
   const int planes = io->na > 0 ? 2 : 1;
@@ -594,11 +591,11 @@ int launch(int m, int n, int k, const void* a_codes, const void* w_codes, const 
   p.kb = k / 128; p.nb = n / 128; p.mb = (m + 127) / 128;
   p.tiles_n = (n + BN - 1) / BN;
   p.tiles = p.mb * p.tiles_n;
-  static bool configured = false;
-  if (!configured) {
+  static std::atomic<bool> configured[64];       // the shared-memory opt-in is a per-device attribute of the function
+  if (!configured[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(fused_kernel<BN, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
       return TW_ERR_LAUNCH;
-    configured = true;
+    configured[dev].store(true, std::memory_order_release);
   }
   const int grid = p.tiles < sms ? p.tiles : sms;
   fused_kernel<BN, DEEP><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tm_a0, tm_a1, tm_w0, tm_w1, p);
@@ -620,7 +617,7 @@ extern "C" int tw_fused(int m, int n, int k, const void* a_codes, const void* w_
   if (io->m != m || io->n != n || io->k != k || io->mp != (m + 15) / 16 * 16) return TW_ERR_SHAPE;
   if (io->na < 0 || io->na > k / 128) return TW_ERR_ARGUMENT;
   if (io->na > 0 && !io->a1s_swz) return TW_ERR_MISSING_SWIZZLED;
-  if (io->na > 0 && io->na < k / 128 && !io->mask) return TW_ERR_ARGUMENT;
+  if (io->na > 0 && (io->mask_per_n || io->na < k / 128) && !io->mask) return TW_ERR_ARGUMENT;
   if (io->hasw) {
     if (!io->wr || !io->wrs_swz) return TW_ERR_MISSING_SWIZZLED;
     if (io->bank_blocks <= 0) return TW_ERR_ARGUMENT;
@@ -629,10 +626,12 @@ extern "C" int tw_fused(int m, int n, int k, const void* a_codes, const void* w_
   }
   const uintptr_t align = (uintptr_t)a_codes | (uintptr_t)w_codes | (uintptr_t)sfa | (uintptr_t)sfb | (uintptr_t)out |
                           (uintptr_t)io->a1s_swz | (uintptr_t)io->wrs_swz | (uintptr_t)io->wr;
-  if (align & 15) return TW_ERR_ALIGNMENT;
+  // TMA bases and bulk copies: 16 bytes; bias rows are read as 16-byte vectors; output rows are written
+  // with 32-byte stores
+  if ((align & 15) || ((uintptr_t)io->bias & 15) || ((uintptr_t)out & 31)) return TW_ERR_ALIGNMENT;
   if (!encode_fn()) return TW_ERR_DRIVER;
   int dev = 0, sms = 0, major = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return TW_ERR_LAUNCH;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TW_ERR_LAUNCH;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
   if (major != 10) return TW_ERR_ARCH;
@@ -640,8 +639,8 @@ extern "C" int tw_fused(int m, int n, int k, const void* a_codes, const void* w_
   if (n % 256 == 0 && !io->mask_per_n) {
     // with W1 tiles and an A1 quota of at least half the K blocks the unit rings are the scarcer resource
     // (2x plan: +1 %), below that the third base stage is (1.5x plan: +1.3 %, base plan: +16 %)
-    if (io->hasw && 2 * io->na >= k / 128) return launch<256, true>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms);
-    return launch<256, false>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms);
+    if (io->hasw && 2 * io->na >= k / 128) return launch<256, true>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms, dev);
+    return launch<256, false>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms, dev);
   }
-  return launch<128, false>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms);
+  return launch<128, false>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms, dev);
 }

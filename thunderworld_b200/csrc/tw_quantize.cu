@@ -5,6 +5,7 @@
 // (thunderworld_fp4/cosmos/calibration.py:30-54, _quantize.py:81-107, _calibrated.py:11-38):
 // IEEE fp32 division, E4M3 and E2M1 round-to-nearest-even, residual taken from the rounded base.
 #include <type_traits>
+#include <atomic>
 #include "tw_common.cuh"
 #include "../../include/twb200.h"
 
@@ -108,28 +109,6 @@ __device__ __forceinline__ float2 e2m1x2_values(uint32_t byte) {
   uint32_t h2;
   asm("{ .reg .b8 t; cvt.u8.u32 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(h2) : "r"(byte));
   return __half22float2(*reinterpret_cast<__half2*>(&h2));
-}
-
-// One group of 16 values: scale byte + 8 code bytes; optionally the dequantized values.
-__device__ __forceinline__ uint32_t encode_group(const float (&z)[16], float multiplier, uint2& codes,
-                                                 float& scale_value) {
-  float peak = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) peak = fmaxf(peak, fabsf(z[i]));
-  float raw = __fdiv_rn(__fmul_rn(peak, multiplier), 6.f);
-  raw = fminf(fmaxf(raw, 0.001953125f), 448.f);
-  uint32_t sb = tw::f32_to_e4m3(raw);
-  float s = tw::e4m3_to_f32(sb);
-  const float rs = __frcp_rn(s);
-  uint32_t w[2] = {0u, 0u};
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    uint32_t b = tw::f32x2_to_e2m1x2(div_by(z[2 * i], s, rs), div_by(z[2 * i + 1], s, rs));
-    w[i >> 2] |= b << (8 * (i & 3));
-  }
-  codes = make_uint2(w[0], w[1]);
-  scale_value = s;
-  return sb;
 }
 
 __device__ __forceinline__ uint32_t scale_offset(int row, int col, int cols) {
@@ -424,25 +403,26 @@ namespace {
 constexpr int STATIC_TILES = 16384;                       // lattice tiles: ceil(m/128) * (k/128) <= 16384
 static __device__ __align__(256) unsigned char g_quantize_scratch[256 + STATIC_TILES * sizeof(float)];
 constexpr int MAX_DEVICES = 64;
-void* g_scratch_address[MAX_DEVICES] = {};
+std::atomic<void*> g_scratch_address[MAX_DEVICES];      // zero-initialised; host threads may race to fill a slot
 }  // namespace
 
 extern "C" int tw_quantize_static_max_tiles(void) { return STATIC_TILES; }
 
 extern "C" int tw_quantize_static(const TwQuantizeArgs* a, void* stream) {
   if (!a) return TW_ERR_ARGUMENT;
-  if (a->m <= 0 || a->k <= 0 || a->k % 128) return a->k % 128 ? TW_ERR_SHAPE : TW_ERR_ARGUMENT;
+  if (a->m <= 0 || a->k <= 0) return TW_ERR_ARGUMENT;
+  if (a->k % 128) return TW_ERR_SHAPE;
   const long long tiles = (long long)((a->m + 127) / 128) * (a->k / 128);
   if (tiles > STATIC_TILES) return TW_ERR_TOO_LARGE;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return TW_ERR_LAUNCH;
-  if (!g_scratch_address[dev]) {
+  void* ptr = g_scratch_address[dev].load(std::memory_order_acquire);
+  if (!ptr) {
     // first call on this device (it is the current one): resolve the device address of the array
-    void* ptr = nullptr;
     if (cudaGetSymbolAddress(&ptr, g_quantize_scratch) != cudaSuccess || !ptr) return TW_ERR_LAUNCH;
-    g_scratch_address[dev] = ptr;
+    g_scratch_address[dev].store(ptr, std::memory_order_release);
   }
   TwQuantizeArgs local = *a;
-  local.workspace = g_scratch_address[dev];
+  local.workspace = ptr;
   return tw_quantize(&local, stream);
 }

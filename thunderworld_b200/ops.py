@@ -148,11 +148,32 @@ def fused_gemm(m, n, k, packed, wc, ws_swz, alpha, *, na=0, mask=None, wr=None, 
     return out
 
 
+STATUS_KEYS = ('g', 'a')       # workspaces whose first word is a device status word: fused GEMM, attention
+
+
 def device_status(device=None):
-    """Read the status word the GEMM kernels write on a bounded-wait timeout (synchronises)."""
-    dev = torch.device('cuda', torch.cuda.current_device()) if device is None else device
-    ws = _workspaces.get((dev, 'g'))
-    return 0 if ws is None else int(ws[:4].view(torch.int32).item())
+    """Worst status word any kernel of this device wrote on a bounded-wait timeout (0 = none); synchronises.
+    Covers the fused GEMM and the attention kernel: each writes into the first word of its own workspace."""
+    dev = torch.device('cuda', torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev.index is None:
+        dev = torch.device('cuda', torch.cuda.current_device())
+    worst = 0
+    for key in STATUS_KEYS:
+        ws = _workspaces.get((dev, key))
+        if ws is not None:
+            worst = max(worst, int(ws[:4].view(torch.int32).item()))
+    return worst
+
+
+def reset_device_status(device=None):
+    """Clear the status words (after a reported timeout has been handled)."""
+    dev = torch.device('cuda', torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev.index is None:
+        dev = torch.device('cuda', torch.cuda.current_device())
+    for key in STATUS_KEYS:
+        ws = _workspaces.get((dev, key))
+        if ws is not None:
+            ws[:4].zero_()
 
 
 # ---- pointwise producers with fused tensor factor -----------------------------------------------
