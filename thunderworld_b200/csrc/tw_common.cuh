@@ -74,6 +74,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
+// Non-blocking poll of a phase: issued ahead of use so that its latency hides behind other instructions.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
 // Bounded wait: polls until the phase with `parity` completes, the CTA-wide
 // abort flag is raised, or about `limit_cycles` SM cycles (about half a second) have passed. On a
 // timeout it raises the abort flag and returns false; it never traps.
@@ -89,6 +97,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       if (clock64() - start > limit_cycles) { *abort_flag = 1; return false; }
     }
   }
+}
+
+// Same contract for a whole, converged warp: every lane polls (the barrier state is the same for all
+// lanes of one instruction), so control flow stays warp-uniform around the wait and the elected lane
+// that issues the asynchronous operations afterwards does so from converged code.
+__device__ __forceinline__ bool mbar_wait_all(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                              long long limit_cycles = 1000000000LL) {
+  if (mbar_try_wait(bar, parity)) return true;     // the common case: one instruction, same answer in every lane
+  bool ok = true;
+  long long start = clock64();
+  uint32_t polls = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++polls & 255u) == 0u) {
+      if (*abort_flag) { ok = false; break; }
+      if (clock64() - start > limit_cycles) { *abort_flag = 1; ok = false; break; }
+    }
+  }
+  __syncwarp();
+  return __all_sync(0xffffffffu, ok);
+}
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{ .reg .pred p; elect.sync _|p, 0xffffffff; selp.u32 %0, 1, 0, p; }" : "=r"(pred));
+  return pred != 0;
 }
 
 // Same contract, for warps that wait long (epilogue, table builder): only lane 0 polls, with a

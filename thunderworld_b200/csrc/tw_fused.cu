@@ -7,18 +7,25 @@
 // scales by the device scalar alpha and rounds to bf16 once. Term structure follows the reference
 // (thunderworld_fp4/_native.py:11-62; cutlass/repair_collective.cuh:117-132); what differs is the
 // schedule. The K loop advances in steps of 256 (two blocks of the K128 repair lattice): a "base
-// stage" holds A0 (128 x 128 B) and W0 (BN x 128 B) of the step with their scales and costs the
-// single-thread producer and MMA roles one barrier round trip; the repair operands of the same
-// step (A1 blocks, W1 tiles: "units" of 128 x 64 B) arrive through a second ring and are multiplied
-// against the resident base stage, so W0 is fetched once for A0 and A1, and A0 once for W0 and W1.
+// stage" holds A0 (128 x 128 B) and W0 (BN x 128 B) of the step with their scales; the repair
+// operands of the same step (A1 blocks, W1 tiles: "units" of 128 x 64 B) arrive through a second
+// ring and are multiplied against the resident base stage, so W0 is fetched once for A0 and A1,
+// and A0 once for W0 and W1.
 //
-// CTA = one 128 x BN output tile at a time (persistent over tiles), warp-specialised:
+// CTA = one 128 x BN output tile at a time (persistent over tiles), warp-specialised. Every role
+// runs as a whole, converged warp and elects one lane only around the asynchronous instructions
+// (TMA, tcgen05.cp / .mma / .commit): issued from a divergent single-lane branch the same
+// instructions cost the issuing thread tens of cycles each and the tensor pipe starves.
 //   warp 0      producer of base stages (TMA, 128-byte swizzle; bulk copies of scale atoms)
-//   warp 1      MMA issuer: MMAs, scale copies of repair units, commits
+//   warp 1      MMA issuer: scale copies smem -> TMEM (tcgen05.cp), MMAs, commits
 //   warps 2, 6  producers of repair units (A1 blocks / W1 tiles; TMA, 64-byte swizzle)
 //   warp 3      builds the per-tile term tables (A-support bits, W1 bank positions) ahead of use
-//   warps 4,5   copy the base-stage scale atoms smem -> TMEM (tcgen05.cp) ahead of the MMA issuer
 //   warps 8-15  epilogue: TMEM -> registers -> bf16 -> global (32-byte stores)
+// Tensor memory: two accumulators whose column ranges overlap by 64 ([0,256) and [192,448) for
+// 256-wide tiles) plus 64 columns of scale factors. The epilogue of a tile drains the shared
+// columns first and then tells the MMA issuer, so the next tile's MMAs run under the rest of the
+// drain. tcgen05.cp and tcgen05.mma of one thread execute in issue order, so each scale region is
+// single and is rewritten for the next step without a barrier.
 // No cluster, no multicast.
 #include <atomic>
 #include <cuda.h>
@@ -31,21 +38,19 @@ constexpr int KB_MAX = 192;               // K <= 24576
 constexpr int UNIT_TILE = 128 * 64;       // bytes of one 128-row x K128 code tile
 constexpr int SF_ATOM = 1024;             // bytes of the scales of 128 rows x K128
 
-// DEEP = true trades one base stage for deeper repair-unit rings: at the 2x plan a K256 step takes long
-// enough for two base stages, and the issuer waits less for unit scales; without repair terms the third
-// base stage is worth 16 %. The host picks the variant from the plan.
+// DEEP = true trades one base stage for deeper repair-unit rings (plans with W1 tiles and an A1 quota of at
+// least half the K blocks); without repair terms the third base stage is worth more. The host picks.
 template <int BN, bool DEEP = false> struct Cfg {
   static constexpr int HALVES = BN / 128;
   static constexpr int STAGES = BN == 256 ? (DEEP ? 2 : 3) : 4;   // base stages (K256 of A0 and W0)
-  static constexpr int A1_SLOTS = DEEP && BN == 256 ? 4 : 3;      // A1 units
-  static constexpr int W1_SLOTS = DEEP && BN == 256 ? 6 : 3;      // W1 units
+  static constexpr int A1_SLOTS = BN == 256 ? (DEEP ? 4 : 2) : 3;  // A1 units
+  static constexpr int W1_SLOTS = BN == 256 ? (DEEP ? 6 : 4) : 3;  // W1 units
   static constexpr int TAB_SLOTS = 3;                         // per-tile term tables built ahead
-  static constexpr int ACC_STAGES = BN == 256 ? 1 : 2;
   static constexpr int EPI_WARPS = 8;
-  static constexpr int FIRST_EPI_WARP = 8;                    // warps 0-3 and 4-5 are single-thread roles, 6-7 idle
-  static constexpr int SF_THREADS = 2;                        // threads that copy base-stage scales into TMEM
+  static constexpr int FIRST_EPI_WARP = 8;                    // warps 0-3 and 6 are control roles, 4, 5, 7 idle
   static constexpr int EPI_GROUPS = EPI_WARPS / 4;            // column groups per lane quadrant
   static constexpr int EPI_COLS = BN / EPI_GROUPS;            // columns per epilogue warp
+  static constexpr int EPI_ROUNDS = EPI_COLS / 64;
   static constexpr int THREADS = (FIRST_EPI_WARP + EPI_WARPS) * 32;
   static constexpr int A0_TILE = 128 * 128;                   // 128 rows x K256
   static constexpr int W0_TILE = BN * 128;
@@ -61,16 +66,20 @@ template <int BN, bool DEEP = false> struct Cfg {
   static constexpr int OFF_TAB = OFF_SFW1 + W1_SLOTS * SF_ATOM;
   static constexpr int TAB_BYTES = HALVES * KB_MAX * 4 + (HALVES + 1) * (KB_MAX / 32) * 4;
   static constexpr int OFF_BAR = OFF_TAB + TAB_SLOTS * TAB_BYTES;
-  static constexpr int NUM_BARS = 2 * STAGES + 2 * A1_SLOTS + 2 * W1_SLOTS + 2 * TAB_SLOTS + 2 * ACC_STAGES + STAGES + A1_SLOTS + W1_SLOTS;
+  static constexpr int NUM_BARS = 2 * STAGES + A1_SLOTS + W1_SLOTS + 2 * TAB_SLOTS + 2 + 1;
   static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 64 + 1024;  // + alignment slack
-  // tensor-memory columns: accumulators, then double-buffered scale regions
-  static constexpr int TM_ACC = 0;
-  static constexpr int TM_SFA0 = ACC_STAGES * BN;                        // STAGES x 16 columns: one region per smem stage
-  static constexpr int TM_SFB0 = TM_SFA0 + 16 * STAGES;                  // STAGES x 16*HALVES columns
-  static constexpr int TM_SFA1 = TM_SFB0 + 16 * HALVES * STAGES;                  // 8 columns per A1 slot
-  static constexpr int TM_SFW1 = TM_SFA1 + 32;                           // 8 columns per W1 slot
+  // tensor-memory columns: two accumulators (tile i uses accumulator i & 1) that share the columns
+  // [ACC_STRIDE, BN), then the scale regions
+  static constexpr int ACC_STRIDE = BN == 256 ? 192 : 128;
+  static constexpr int TM_SF = ACC_STRIDE + BN;                          // 448 (256 for 128-wide tiles)
+  static constexpr int TM_SFA0 = TM_SF;                                  // 16 columns: A0 scales of the step
+  static constexpr int TM_SFB0 = TM_SFA0 + 16;                           // 16 * HALVES: W0 scales of the step
+  static constexpr int TM_SFA1 = TM_SFB0 + 16 * HALVES;                  // 8: the A1 block being multiplied
+  static constexpr int TM_SFW1 = TM_SFA1 + 8;                            // 8: the W1 tile being multiplied
   static constexpr int TM_COLS = 512;
-  static_assert(A1_SLOTS * 8 <= 32 && TM_SFW1 + 8 * W1_SLOTS <= TM_COLS, "tensor memory budget");
+  static_assert(TM_SFW1 + 8 <= TM_COLS, "tensor memory budget");
+  // a step is issued only when all its units have landed, so the rings must hold the units of one step
+  static_assert(A1_SLOTS >= 2 && W1_SLOTS >= 2 * HALVES, "unit rings hold at least one step");
 };
 static_assert(Cfg<256>::SMEM_BYTES <= 232448 && Cfg<256, true>::SMEM_BYTES <= 232448 && Cfg<128>::SMEM_BYTES <= 232448,
               "shared memory budget");
@@ -146,20 +155,15 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
-  uint64_t* fullS = bars;                       // base stages
-  uint64_t* emptyS = fullS + C::STAGES;
-  uint64_t* fullA1 = emptyS + C::STAGES;        // A1 units
-  uint64_t* emptyA1 = fullA1 + C::A1_SLOTS;
-  uint64_t* fullW1 = emptyA1 + C::A1_SLOTS;     // W1 units
-  uint64_t* emptyW1 = fullW1 + C::W1_SLOTS;
+  uint64_t* fullS = bars;                       // a step's operands (base stage and its repair units) have landed
+  uint64_t* emptyS = fullS + C::STAGES;         // the MMAs that read the base stage have completed
+  uint64_t* emptyA1 = emptyS + C::STAGES;       // the MMAs that read an A1 / W1 unit slot have completed
+  uint64_t* emptyW1 = emptyA1 + C::A1_SLOTS;
   uint64_t* tabFull = emptyW1 + C::W1_SLOTS;
   uint64_t* tabEmpty = tabFull + C::TAB_SLOTS;
-  uint64_t* accFull = tabEmpty + C::TAB_SLOTS;
-  uint64_t* accEmpty = accFull + C::ACC_STAGES;
-  uint64_t* sfFull = accEmpty + C::ACC_STAGES;   // scales of the base stage in slot i are in its TMEM region
-  uint64_t* usfA = sfFull + C::STAGES;                  // scales of the A1 unit in slot i are in TMEM
-  uint64_t* usfW = usfA + C::A1_SLOTS;           // same for W1 units
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(usfW + C::W1_SLOTS);
+  uint64_t* accFull = tabEmpty + C::TAB_SLOTS;  // [2]: every term of the tile in accumulator a has been accumulated
+  uint64_t* sharedFree = accFull + 2;           // the epilogue has read the columns both accumulators share
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sharedFree + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   auto table = [&](uint32_t i) -> TermTable<BN>& {
     return *reinterpret_cast<TermTable<BN>*>(smem + C::OFF_TAB + (i % C::TAB_SLOTS) * C::TAB_BYTES);
@@ -169,14 +173,12 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
   const int steps = (p.kb + 1) / 2;             // K256 steps; the last one may hold a single K128 block
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < C::STAGES; ++i) { tw::mbar_init(fullS + i, 1); tw::mbar_init(emptyS + i, 1); }
-    for (int i = 0; i < C::A1_SLOTS; ++i) { tw::mbar_init(fullA1 + i, 1); tw::mbar_init(emptyA1 + i, 1); }
-    for (int i = 0; i < C::W1_SLOTS; ++i) { tw::mbar_init(fullW1 + i, 1); tw::mbar_init(emptyW1 + i, 1); }
-    for (int i = 0; i < C::TAB_SLOTS; ++i) { tw::mbar_init(tabFull + i, 1); tw::mbar_init(tabEmpty + i, 3 + C::SF_THREADS); }
-    for (int i = 0; i < C::ACC_STAGES; ++i) { tw::mbar_init(accFull + i, 1); tw::mbar_init(accEmpty + i, C::EPI_WARPS); }
-    for (int i = 0; i < C::STAGES; ++i) tw::mbar_init(sfFull + i, C::SF_THREADS);
-    for (int i = 0; i < C::A1_SLOTS; ++i) tw::mbar_init(usfA + i, 1);
-    for (int i = 0; i < C::W1_SLOTS; ++i) tw::mbar_init(usfW + i, 1);
+    for (int i = 0; i < C::STAGES; ++i) { tw::mbar_init(fullS + i, 3); tw::mbar_init(emptyS + i, 1); }
+    for (int i = 0; i < C::A1_SLOTS; ++i) tw::mbar_init(emptyA1 + i, 1);
+    for (int i = 0; i < C::W1_SLOTS; ++i) tw::mbar_init(emptyW1 + i, 1);
+    for (int i = 0; i < C::TAB_SLOTS; ++i) { tw::mbar_init(tabFull + i, 1); tw::mbar_init(tabEmpty + i, 3); }
+    tw::mbar_init(accFull, 1); tw::mbar_init(accFull + 1, 1);
+    tw::mbar_init(sharedFree, C::EPI_WARPS);
     *abort_flag = 0;
     tw::fence_barrier_init();
     tw::tma_prefetch_desc(&tm_a0); tw::tma_prefetch_desc(&tm_a1);
@@ -199,17 +201,16 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
   } else if (warp == 0) {
     // ------------------------------------------------------------------ producer of base stages
     // Needs no term table: one stage per K256 step of every tile.
-    if (lane == 0) {
-      uint32_t is = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x) {
-        const int mbi = tile / p.tiles_n, nt = tile % p.tiles_n;
-        const int n_rows = min(BN, p.n - nt * BN);            // 128 or BN
-        for (int st = 0; st < steps && ok; ++st, ++is) {
-          const uint32_t s = is % C::STAGES, ph = (is / C::STAGES) & 1;
-          const int kb0 = 2 * st, nk = min(2, p.kb - kb0);     // K128 blocks in this step
-          ok = tw::mbar_wait(emptyS + s, ph ^ 1, abort_flag);
-          if (!ok) break;
+    uint32_t s = 0, ph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x) {
+      const int mbi = tile / p.tiles_n, nt = tile % p.tiles_n;
+      const int n_rows = min(BN, p.n - nt * BN);            // 128 or BN
+      for (int st = 0; st < steps && ok; ++st) {
+        const int kb0 = 2 * st, nk = min(2, p.kb - kb0);     // K128 blocks in this step
+        ok = tw::mbar_wait_all(emptyS + s, ph ^ 1, abort_flag);
+        if (!ok) break;
+        if (tw::elect_one()) {
           // TMA always delivers the full box (out-of-range K reads as zero codes)
           tw::mbar_expect_tx(fullS + s, C::A0_TILE + (uint32_t)n_rows * 128 + (uint32_t)(1 + n_rows / 128) * nk * SF_ATOM);
           tw::tma_load_3d(smem + C::OFF_A0 + s * C::A0_TILE, &tm_a0, kb0 * 64, mbi * 128, 0, fullS + s);
@@ -220,213 +221,137 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
             tw::bulk_load(sf + (1 + h) * 2 * SF_ATOM, p.sfb0 + ((size_t)(nt * C::HALVES + h) * p.kb + kb0) * SF_ATOM,
                           nk * SF_ATOM, fullS + s);
         }
+        __syncwarp();
+        if (++s == C::STAGES) { s = 0; ph ^= 1; }
       }
     }
   } else if (warp == 2 || warp == 6) {
     // ------------------------------------------------------------------ producers of repair units
-    // Per step, in the order the MMA issuer consumes them: A1(kb0), A1(kb1) by warp 2, W1 tiles by
-    // (kb, half) by warp 6: a full W1 ring does not hold the A1 loads of the next step back.
-    if (lane == 0) {
-      const bool do_a = warp == 2, do_w = warp == 6;
-      uint32_t ia = 0, iw = 0, it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
-        const int mbi = tile / p.tiles_n;
-        const TermTable<BN>& tab = table(it);
-        ok = tw::mbar_wait(tabFull + it % C::TAB_SLOTS, (it / C::TAB_SLOTS) & 1, abort_flag);
-        uint32_t abits = 0, wbits[C::HALVES] = {};
-        for (int st = 0; st < steps && ok; ++st) {
-          const int kb0 = 2 * st;
-          if ((kb0 & 31) == 0) {
-            abits = tab.a1bits[kb0 >> 5];
+    // Warp 2 loads the A1 blocks, warp 6 the W1 tiles of every step, in the order the MMA issuer consumes
+    // them. Their bytes complete on the step's stage barrier (it counts three arrivals: the base producer
+    // and these two, with or without units), so the issuer waits once per step; slots are recycled through
+    // their own barriers, which the issuer commits after the unit's last MMA.
+    const bool do_a = warp == 2;
+    uint32_t s = 0, ph = 0, sa = 0, pa = 0, sw = 0, pw = 0, it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
+      const int mbi = tile / p.tiles_n;
+      const TermTable<BN>& tab = table(it);
+      ok = tw::mbar_wait_all(tabFull + it % C::TAB_SLOTS, (it / C::TAB_SLOTS) & 1, abort_flag);
+      uint32_t abits = 0, wbits[C::HALVES] = {};
+      for (int st = 0; st < steps && ok; ++st) {
+        const int kb0 = 2 * st;
+        if ((kb0 & 31) == 0) {
+          abits = tab.a1bits[kb0 >> 5];
 #pragma unroll
-            for (int h = 0; h < C::HALVES; ++h) wbits[h] = tab.w1bits[h][kb0 >> 5];
-          }
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            if (!do_a || !((abits >> j) & 1u) || !ok) continue;
-            const uint32_t s = ia % C::A1_SLOTS, ph = (ia / C::A1_SLOTS) & 1; ++ia;
-            ok = tw::mbar_wait(emptyA1 + s, ph ^ 1, abort_flag);
-            if (!ok) continue;
-            tw::mbar_expect_tx(fullA1 + s, UNIT_TILE + SF_ATOM);
-            tw::tma_load_3d(smem + C::OFF_A1 + s * UNIT_TILE, &tm_a1, (kb0 + j) * 64, mbi * 128, 1, fullA1 + s);
-            tw::bulk_load(smem + C::OFF_SFA1 + s * SF_ATOM, p.sfa1 + ((size_t)mbi * p.kb + kb0 + j) * SF_ATOM, SF_ATOM, fullA1 + s);
-          }
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-#pragma unroll
-            for (int h = 0; h < C::HALVES; ++h) {
-              if (!do_w || !((wbits[h] >> j) & 1u) || !ok) continue;
-              const int loc = tab.w1loc[h][kb0 + j];
-              const uint32_t s = iw % C::W1_SLOTS, ph = (iw / C::W1_SLOTS) & 1; ++iw;
-              ok = tw::mbar_wait(emptyW1 + s, ph ^ 1, abort_flag);
-              if (!ok) continue;
-              tw::mbar_expect_tx(fullW1 + s, UNIT_TILE + SF_ATOM);
-              tw::tma_load_2d(smem + C::OFF_W1 + s * UNIT_TILE, &tm_w1, 0, loc * 128, fullW1 + s);
-              tw::bulk_load(smem + C::OFF_SFW1 + s * SF_ATOM, p.sfbw + (size_t)loc * SF_ATOM, SF_ATOM, fullW1 + s);
-            }
-          }
-          abits >>= 2;
-#pragma unroll
-          for (int h = 0; h < C::HALVES; ++h) wbits[h] >>= 2;
+          for (int h = 0; h < C::HALVES; ++h) wbits[h] = tab.w1bits[h][kb0 >> 5];
         }
-        tw::mbar_arrive(tabEmpty + it % C::TAB_SLOTS);
+        uint32_t mine = 0;                                     // bit 2j + h: unit of block j (half h for W1)
+        if (do_a) mine = (abits & 1u) | ((abits & 2u) << 1);
+        else {
+#pragma unroll
+          for (int h = 0; h < C::HALVES; ++h) mine |= ((wbits[h] & 1u) << h) | ((wbits[h] & 2u) << (1 + h));
+        }
+        ok = tw::mbar_wait_all(emptyS + s, ph ^ 1, abort_flag);    // the stage barrier is in its next phase
+        if (!ok) break;
+        if (tw::elect_one()) {
+          if (mine) tw::mbar_expect_tx(fullS + s, (uint32_t)__popc(mine) * (UNIT_TILE + SF_ATOM));
+          else tw::mbar_arrive(fullS + s);
+        }
+        __syncwarp();
+#pragma unroll 1
+        while (mine && ok) {
+          const uint32_t u = __ffs(mine) - 1;
+          mine &= mine - 1;
+          const int kb = kb0 + (int)(u >> 1);
+          if (do_a) {
+            ok = tw::mbar_wait_all(emptyA1 + sa, pa ^ 1, abort_flag);
+            if (!ok) break;
+            if (tw::elect_one()) {
+              tw::tma_load_3d(smem + C::OFF_A1 + sa * UNIT_TILE, &tm_a1, kb * 64, mbi * 128, 1, fullS + s);
+              tw::bulk_load(smem + C::OFF_SFA1 + sa * SF_ATOM, p.sfa1 + ((size_t)mbi * p.kb + kb) * SF_ATOM, SF_ATOM, fullS + s);
+            }
+            __syncwarp();
+            if (++sa == C::A1_SLOTS) { sa = 0; pa ^= 1; }
+          } else {
+            const int loc = tab.w1loc[u & 1u][kb];
+            ok = tw::mbar_wait_all(emptyW1 + sw, pw ^ 1, abort_flag);
+            if (!ok) break;
+            if (tw::elect_one()) {
+              tw::tma_load_2d(smem + C::OFF_W1 + sw * UNIT_TILE, &tm_w1, 0, loc * 128, fullS + s);
+              tw::bulk_load(smem + C::OFF_SFW1 + sw * SF_ATOM, p.sfbw + (size_t)loc * SF_ATOM, SF_ATOM, fullS + s);
+            }
+            __syncwarp();
+            if (++sw == C::W1_SLOTS) { sw = 0; pw ^= 1; }
+          }
+        }
+        if (++s == C::STAGES) { s = 0; ph ^= 1; }
+        abits >>= 2;
+#pragma unroll
+        for (int h = 0; h < C::HALVES; ++h) wbits[h] >>= 2;
       }
+      if (tw::elect_one()) tw::mbar_arrive(tabEmpty + it % C::TAB_SLOTS);
+      __syncwarp();
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer (one thread)
-    // One thread issues every tcgen05 operation, so its instruction stream is kept short: slot
-    // counters advance incrementally, descriptors are a constant high word plus (address >> 4).
-    if (lane == 0) {
-      bool ok = true;
-      constexpr uint32_t IDESC_FULL = tw::make_idesc_nvf4(128, BN);
-      constexpr uint32_t IDESC_128 = tw::make_idesc_nvf4(128, 128);
-      constexpr uint64_t D128 = (uint64_t(1) << 46) | (uint64_t(2) << 61) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 16);
-      constexpr uint64_t D64 = (uint64_t(1) << 46) | (uint64_t(4) << 61) | (uint64_t(512 >> 4) << 32) | (uint64_t(1) << 16);
-      constexpr uint64_t DSF = (uint64_t(1) << 46) | (uint64_t(128 >> 4) << 32);
-      const uint32_t smem_u = tw::smem_u32(smem);
-      const uint32_t a0_base = (smem_u + C::OFF_A0) >> 4, w0_base = (smem_u + C::OFF_W0) >> 4;
-      const uint32_t a1_base = (smem_u + C::OFF_A1) >> 4, w1_base = (smem_u + C::OFF_W1) >> 4;
-      const uint32_t t_sfa0_b = tmem + C::TM_SFA0, t_sfb0_b = tmem + C::TM_SFB0;
-      uint32_t s = 0, ph = 0;                  // base stage slot / phase
-      uint32_t sa = 0, pa = 0, sw = 0, pw = 0; // unit slots / phases
-      uint32_t it = 0, tsl = 0, tph = 0;       // tile counter, table slot / phase
-      for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
-        const int nt = tile % p.tiles_n;
-        const TermTable<BN>& tab = *reinterpret_cast<const TermTable<BN>*>(smem + C::OFF_TAB + tsl * C::TAB_BYTES);
-        const int n_rows = min(BN, p.n - nt * BN);
-        const uint32_t idesc_base = n_rows == BN ? IDESC_FULL : IDESC_128;
-        const uint32_t stage = it % C::ACC_STAGES, aph = (it / C::ACC_STAGES) & 1;
-        ok = tw::mbar_wait(tabFull + tsl, tph, abort_flag) && tw::mbar_wait(accEmpty + stage, aph ^ 1, abort_flag);
-        tw::tc_fence_after();
-        const uint32_t acc = tmem + C::TM_ACC + stage * BN;
-        uint32_t abits = 0, wbits[C::HALVES] = {};
-        for (int st = 0; st < steps && ok; ++st) {
-          const int kb0 = 2 * st;
-          const int nq = p.kb - kb0 >= 2 ? 4 : 2;                  // K64 slices in this step
-          if ((kb0 & 31) == 0) {
-            abits = tab.a1bits[kb0 >> 5];
+    // ------------------------------------------------------------------ MMA issuer
+    // The whole warp walks the schedule (waits are warp-wide, every branch is warp-uniform); one elected
+    // lane issues all tcgen05 operations of a step in one go: scale copies and MMAs of the base stage, then
+    // of its repair units, then the commits that release the stage and the unit slots. The stage barrier
+    // of the next step is polled before the current step is issued, so its latency hides behind the issue.
+    // Descriptors are a constant high word plus (address >> 4).
+    bool ok = true;
+    constexpr uint32_t IDESC_FULL = tw::make_idesc_nvf4(128, BN);
+    constexpr uint32_t IDESC_128 = tw::make_idesc_nvf4(128, 128);
+    constexpr uint64_t D128 = (uint64_t(1) << 46) | (uint64_t(2) << 61) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 16);
+    constexpr uint64_t D64 = (uint64_t(1) << 46) | (uint64_t(4) << 61) | (uint64_t(512 >> 4) << 32) | (uint64_t(1) << 16);
+    constexpr uint64_t DSF = (uint64_t(1) << 46) | (uint64_t(128 >> 4) << 32);
+    const uint32_t smem_u = tw::smem_u32(smem);
+    const uint32_t a0_base = (smem_u + C::OFF_A0) >> 4, w0_base = (smem_u + C::OFF_W0) >> 4;
+    const uint32_t a1_base = (smem_u + C::OFF_A1) >> 4, w1_base = (smem_u + C::OFF_W1) >> 4;
+    const uint32_t sf0_base = (smem_u + C::OFF_SF0) >> 4;
+    const uint32_t sfa1_base = (smem_u + C::OFF_SFA1) >> 4, sfw1_base = (smem_u + C::OFF_SFW1) >> 4;
+    const uint32_t t_sfa0 = tmem + C::TM_SFA0, t_sfb0 = tmem + C::TM_SFB0;
+    const uint32_t t_sfa1 = tmem + C::TM_SFA1, t_sfw1 = tmem + C::TM_SFW1;
+    uint32_t s = 0, ph = 0;                  // base stage slot / phase
+    uint32_t sa = 0, sw = 0;                 // next unit slots
+    uint32_t it = 0, tsl = 0, tph = 0;       // tile counter, table slot / phase
+    bool ready = tw::mbar_test_wait(fullS, 0);
+    for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
+      const int nt = tile % p.tiles_n;
+      const TermTable<BN>& tab = *reinterpret_cast<const TermTable<BN>*>(smem + C::OFF_TAB + tsl * C::TAB_BYTES);
+      const int n_rows = min(BN, p.n - nt * BN);
+      const uint32_t idesc_base = n_rows == BN ? IDESC_FULL : IDESC_128;
+      ok = tw::mbar_wait_all(tabFull + tsl, tph, abort_flag);
+      // the previous tile's epilogue has read the columns this accumulator shares with its own
+      if (ok && it > 0) ok = tw::mbar_wait_all(sharedFree, (it - 1) & 1, abort_flag);
+      tw::tc_fence_after();
+      const uint32_t acc = tmem + (it & 1) * C::ACC_STRIDE;
+      uint32_t abits = 0, wbits[C::HALVES] = {};
+      for (int st = 0; st < steps && ok; ++st) {
+        const int kb0 = 2 * st;
+        const int nq = p.kb - kb0 >= 2 ? 4 : 2;                  // K64 slices in this step
+        if ((kb0 & 31) == 0) {
+          abits = tab.a1bits[kb0 >> 5];
 #pragma unroll
-            for (int h = 0; h < C::HALVES; ++h) wbits[h] = tab.w1bits[h][kb0 >> 5];
-          }
-          // the scale-copy threads waited for the stage's data and moved its scales into TMEM
-          ok = tw::mbar_wait(sfFull + s, ph, abort_flag) && tw::mbar_wait(fullS + s, ph, abort_flag);
-          if (!ok) break;
-          tw::tc_fence_after();
-          const uint32_t a0_lo = a0_base + s * (C::A0_TILE >> 4), w0_lo = w0_base + s * (C::W0_TILE >> 4);
-          const uint32_t t_sfa0 = t_sfa0_b + s * 16, t_sfb0 = t_sfb0_b + s * 16 * C::HALVES;
-#pragma unroll
-          for (int q = 0; q < 4; ++q)                              // A0 W0
-            if (q < nq)
-              tw::tc_mma_nvf4(acc, D128 | (a0_lo + 2 * q), D128 | (w0_lo + 2 * q), idesc_base, t_sfa0 + 4 * q,
-                              t_sfb0 + 4 * C::HALVES * q, (st | q) != 0);
-          const uint32_t ab = abits & 3u;
-          uint32_t wb = 0;
-#pragma unroll
-          for (int h = 0; h < C::HALVES; ++h) wb |= (wbits[h] & 3u) << (2 * h);
-          if (ab | wb) {
-            // A1 blocks of this step against the resident W0 stage
-            uint32_t a1_lo[2] = {0, 0}, a1_bar[2] = {0, 0};
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-              if (!((ab >> j) & 1u) || !ok) continue;
-              ok = tw::mbar_wait(usfA + sa, pa, abort_flag);       // data landed and its scales are in TMEM
-              if (!ok) continue;
-              tw::tc_fence_after();
-              a1_lo[j] = a1_base + sa * (UNIT_TILE >> 4);
-              a1_bar[j] = sa;
-              const uint32_t t_sfa1 = tmem + C::TM_SFA1 + sa * 8;
-#pragma unroll
-              for (int c = 0; c < 2; ++c)
-                tw::tc_mma_nvf4(acc, D64 | (a1_lo[j] + 2 * c), D128 | (w0_lo + 4 * j + 2 * c), idesc_base,
-                                t_sfa1 + 4 * c, t_sfb0 + 4 * C::HALVES * (2 * j + c), 1u);
-              if (!p.cross) tw::tc_commit(emptyA1 + sa);
-              if (++sa == C::A1_SLOTS) { sa = 0; pa ^= 1; }
-            }
-            // W1 tiles of this step: 128-column MMAs into the matching half of the accumulator
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-#pragma unroll
-              for (int h = 0; h < C::HALVES; ++h) {
-                if (!((wb >> (2 * h + j)) & 1u) || !ok) continue;
-                ok = tw::mbar_wait(usfW + sw, pw, abort_flag);
-                if (!ok) continue;
-                tw::tc_fence_after();
-                const uint32_t w1_lo = w1_base + sw * (UNIT_TILE >> 4);
-                const uint32_t t_sfw1 = tmem + C::TM_SFW1 + sw * 8;
-#pragma unroll
-                for (int c = 0; c < 2; ++c)
-                  tw::tc_mma_nvf4(acc + h * 128, D128 | (a0_lo + 4 * j + 2 * c), D64 | (w1_lo + 2 * c), IDESC_128,
-                                  t_sfa0 + 4 * (2 * j + c), t_sfw1 + 4 * c, 1u);
-                if (p.cross && ((ab >> j) & 1u)) {
-                  const uint32_t t_sfa1 = tmem + C::TM_SFA1 + a1_bar[j] * 8;
-#pragma unroll
-                  for (int c = 0; c < 2; ++c)
-                    tw::tc_mma_nvf4(acc + h * 128, D64 | (a1_lo[j] + 2 * c), D64 | (w1_lo + 2 * c), IDESC_128,
-                                    t_sfa1 + 4 * c, t_sfw1 + 4 * c, 1u);
-                }
-                tw::tc_commit(emptyW1 + sw);
-                if (++sw == C::W1_SLOTS) { sw = 0; pw ^= 1; }
-              }
-            }
-            if (p.cross) {
-#pragma unroll
-              for (int j = 0; j < 2; ++j)
-                if ((ab >> j) & 1u) tw::tc_commit(emptyA1 + a1_bar[j]);
-            }
-          }
-          tw::tc_commit(emptyS + s);
-          if (++s == C::STAGES) { s = 0; ph ^= 1; }
-          abits >>= 2;
-#pragma unroll
-          for (int h = 0; h < C::HALVES; ++h) wbits[h] >>= 2;
+          for (int h = 0; h < C::HALVES; ++h) wbits[h] = tab.w1bits[h][kb0 >> 5];
         }
-        if (ok) tw::tc_commit(accFull + stage);
-        tw::mbar_arrive(tabEmpty + tsl);
-        if (++tsl == C::TAB_SLOTS) { tsl = 0; tph ^= 1; }
-      }
-    }
-  } else if (warp == 4 || warp == 5) {
-    // ------------------------------------------------------------------ scale copies smem -> TMEM
-    // Issuing a tcgen05.cp costs its thread tens of cycles and a K256 step needs 4 * (1 + BN/128)
-    // of them plus two per repair unit, so they are issued by two threads of their own instead of
-    // the MMA issuer: thread 0 takes K64 slices {0,1} of the base stage and the A1 units, thread 1
-    // slices {2,3} and the W1 units. Every smem stage / unit slot owns a TMEM scale region, which is
-    // free again whenever that stage or slot was reloaded (its previous MMAs had finished by then).
-    if (lane == 0) {
-      const int c = warp - 4;
-      constexpr uint64_t DSF = (uint64_t(1) << 46) | (uint64_t(128 >> 4) << 32);
-      const uint32_t smem_u = tw::smem_u32(smem);
-      const uint32_t sf0_base = (smem_u + C::OFF_SF0) >> 4;
-      const uint32_t usf_base = (smem_u + (c == 0 ? C::OFF_SFA1 : C::OFF_SFW1)) >> 4;
-      const uint32_t t_usf = tmem + (c == 0 ? C::TM_SFA1 : C::TM_SFW1);
-      uint64_t* const unit_full = c == 0 ? fullA1 : fullW1;
-      uint64_t* const unit_ready = c == 0 ? usfA : usfW;
-      const uint32_t unit_slots = c == 0 ? C::A1_SLOTS : C::W1_SLOTS;
-      uint32_t s = 0, ph = 0, su = 0, pu = 0, it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++it) {
-        const int n_rows = min(BN, p.n - (tile % p.tiles_n) * BN);
-        const TermTable<BN>& tab = table(it);
-        ok = tw::mbar_wait(tabFull + it % C::TAB_SLOTS, (it / C::TAB_SLOTS) & 1, abort_flag);
-        uint32_t bits[C::HALVES] = {};
-        for (int st = 0; st < steps && ok; ++st) {
-          const int kb0 = 2 * st, nq = p.kb - kb0 >= 2 ? 4 : 2;
-          if ((kb0 & 31) == 0) {
-            if (c == 0) bits[0] = tab.a1bits[kb0 >> 5];
-            else {
+        // units of this step in issue order: bit 3j = A1 of block j, bit 3j + 1 + h = W1 tile (block j, half h)
+        uint32_t units = (abits & 1u) | ((abits & 2u) << 2);
 #pragma unroll
-              for (int h = 0; h < C::HALVES; ++h) bits[h] = tab.w1bits[h][kb0 >> 5];
-            }
-          }
-          // the stage was reloaded only after the MMAs of its previous use finished, so its region is free
-          ok = tw::mbar_wait(fullS + s, ph, abort_flag);
-          if (!ok) break;
-          const uint32_t sf_lo = sf0_base + s * (C::STAGE_SF >> 4);
-          const uint32_t t_sfa0 = tmem + C::TM_SFA0 + s * 16, t_sfb0 = tmem + C::TM_SFB0 + s * 16 * C::HALVES;
+        for (int h = 0; h < C::HALVES; ++h) units |= ((wbits[h] & 1u) << (1 + h)) | ((wbits[h] & 2u) << (3 + h));
+        // operands arrive through the async proxy (TMA) and are consumed by it (tcgen05): no fence is needed
+        if (!ready) ok = tw::mbar_wait_all(fullS + s, ph, abort_flag);
+        if (!ok) break;
+        {
+          const uint32_t sn = s + 1 == C::STAGES ? 0 : s + 1;
+          ready = tw::mbar_test_wait(fullS + sn, sn == 0 ? ph ^ 1 : ph);
+        }
+        const uint32_t a0_lo = a0_base + s * (C::A0_TILE >> 4), w0_lo = w0_base + s * (C::W0_TILE >> 4);
+        const uint32_t sf_lo = sf0_base + s * (C::STAGE_SF >> 4);
+        if (tw::elect_one()) {
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const int q = 2 * c + i;
+          for (int q = 0; q < 4; ++q) {
             if (q < nq) {
               tw::tc_copy_scales(t_sfa0 + 4 * q, DSF | (sf_lo + q * 32));
 #pragma unroll
@@ -435,29 +360,67 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
                   tw::tc_copy_scales(t_sfb0 + 4 * C::HALVES * q + 4 * h, DSF | (sf_lo + (1 + h) * 128 + q * 32));
             }
           }
-          tw::tc_commit(sfFull + s);
-          if (++s == C::STAGES) { s = 0; ph ^= 1; }
-          // units of this step, in the order the MMA issuer consumes them
-          int count = 0;
-          if (c == 0) count = __popc(bits[0] & 3u);
-          else {
 #pragma unroll
-            for (int h = 0; h < C::HALVES; ++h) count += __popc(bits[h] & 3u);
+          for (int q = 0; q < 4; ++q)                              // A0 W0
+            if (q < nq)
+              tw::tc_mma_nvf4(acc, D128 | (a0_lo + 2 * q), D128 | (w0_lo + 2 * q), idesc_base, t_sfa0 + 4 * q,
+                              t_sfb0 + 4 * C::HALVES * q, (st | q) != 0);
+          // Repair terms of the two K128 blocks of this step, block by block: A1 W0, then per W1 tile A0 W1
+          // (128-column MMAs into the matching half of the accumulator) and, with `cross`, A1 W1. One rolled
+          // loop over the units that exist: the instruction footprint of a step stays small, which matters
+          // because a taken branch over a long unrolled body costs this warp an instruction-cache miss.
+          uint32_t todo = units, la = sa, lw = sw, a1_lo = 0;
+#pragma unroll 1
+          while (todo) {
+            const uint32_t u = __ffs(todo) - 1;
+            todo &= todo - 1;
+            const uint32_t j = u >= 3 ? 1u : 0u, t = u - 3 * j;
+            if (t == 0) {                                          // A1 block j against the resident W0 stage
+              a1_lo = a1_base + la * (UNIT_TILE >> 4);
+              const uint32_t usf = sfa1_base + la * (SF_ATOM >> 4);
+              const uint32_t b_lo = w0_lo + 4 * j, sfb = t_sfb0 + 8 * C::HALVES * j;
+              tw::tc_copy_scales(t_sfa1, DSF | usf);
+              tw::tc_copy_scales(t_sfa1 + 4, DSF | (usf + 32));
+              tw::tc_mma_nvf4(acc, D64 | a1_lo, D128 | b_lo, idesc_base, t_sfa1, sfb, 1u);
+              tw::tc_mma_nvf4(acc, D64 | (a1_lo + 2), D128 | (b_lo + 2), idesc_base, t_sfa1 + 4, sfb + 4 * C::HALVES, 1u);
+              // without a cross term nothing reads the block again
+              if (!p.cross) tw::tc_commit(emptyA1 + la);
+              if (++la == C::A1_SLOTS) la = 0;
+            } else {                                               // W1 tile (block j, half t - 1) against A0
+              const uint32_t w1_lo = w1_base + lw * (UNIT_TILE >> 4), usf = sfw1_base + lw * (SF_ATOM >> 4);
+              const uint32_t a_lo = a0_lo + 4 * j, sfa = t_sfa0 + 8 * j, d = acc + (t - 1) * 128;
+              tw::tc_copy_scales(t_sfw1, DSF | usf);
+              tw::tc_copy_scales(t_sfw1 + 4, DSF | (usf + 32));
+              tw::tc_mma_nvf4(d, D128 | a_lo, D64 | w1_lo, IDESC_128, sfa, t_sfw1, 1u);
+              tw::tc_mma_nvf4(d, D128 | (a_lo + 2), D64 | (w1_lo + 2), IDESC_128, sfa + 4, t_sfw1 + 4, 1u);
+              if (p.cross && ((units >> (3 * j)) & 1u)) {
+                tw::tc_mma_nvf4(d, D64 | a1_lo, D64 | w1_lo, IDESC_128, t_sfa1, t_sfw1, 1u);
+                tw::tc_mma_nvf4(d, D64 | (a1_lo + 2), D64 | (w1_lo + 2), IDESC_128, t_sfa1 + 4, t_sfw1 + 4, 1u);
+              }
+              tw::tc_commit(emptyW1 + lw);
+              if (++lw == C::W1_SLOTS) lw = 0;
+            }
           }
-          for (int u = 0; u < count && ok; ++u) {
-            ok = tw::mbar_wait(unit_full + su, pu, abort_flag);
-            if (!ok) break;
-            const uint32_t lo = usf_base + su * (SF_ATOM >> 4);
-            tw::tc_copy_scales(t_usf + su * 8, DSF | lo);
-            tw::tc_copy_scales(t_usf + su * 8 + 4, DSF | (lo + 32));
-            tw::tc_commit(unit_ready + su);
-            if (++su == unit_slots) { su = 0; pu ^= 1; }
+          if (p.cross && (units & 9u)) {                           // a cross term may have read them last
+            tw::tc_commit(emptyA1 + sa);
+            if ((units & 9u) == 9u) tw::tc_commit(emptyA1 + (sa + 1 == C::A1_SLOTS ? 0 : sa + 1));
           }
-#pragma unroll
-          for (int h = 0; h < C::HALVES; ++h) bits[h] >>= 2;
+          tw::tc_commit(emptyS + s);
         }
-        tw::mbar_arrive(tabEmpty + it % C::TAB_SLOTS);
+        __syncwarp();
+        sa = (sa + __popc(units & 9u)) % C::A1_SLOTS;
+        sw = (sw + __popc(units & 54u)) % C::W1_SLOTS;
+        if (++s == C::STAGES) { s = 0; ph ^= 1; }
+        abits >>= 2;
+#pragma unroll
+        for (int h = 0; h < C::HALVES; ++h) wbits[h] >>= 2;
       }
+      if (tw::elect_one()) {
+        if (ok) tw::tc_commit(accFull + (it & 1));
+        tw::mbar_arrive(tabEmpty + tsl);
+      }
+      __syncwarp();
+      if (++tsl == C::TAB_SLOTS) { tsl = 0; tph ^= 1; }
     }
   } else if (warp >= C::FIRST_EPI_WARP) {
     // ------------------------------------------------------------------ epilogue
@@ -467,26 +430,28 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
     uint32_t it = 0;
     for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++it) {
       const int mbi = tile / p.tiles_n, nt = tile % p.tiles_n;
-      const uint32_t stage = it % C::ACC_STAGES, aph = (it / C::ACC_STAGES) & 1;
-      if (!tw::mbar_wait_warp(accFull + stage, aph, abort_flag)) break;
+      const uint32_t a = it & 1;
+      if (!tw::mbar_wait_warp(accFull + a, (it >> 1) & 1, abort_flag)) break;
       tw::tc_fence_after();
-      const uint32_t t_base = tmem + ((uint32_t)(quad * 32) << 16) + C::TM_ACC + stage * BN + group * C::EPI_COLS;
+      const uint32_t t_base = tmem + ((uint32_t)(quad * 32) << 16) + a * C::ACC_STRIDE + group * C::EPI_COLS;
       const int row = mbi * 128 + quad * 32 + lane;
       const int col = nt * BN + group * C::EPI_COLS;
       __nv_bfloat16* dst = p.out + (size_t)row * p.n + col;
       const bool store = row < p.m && col < p.n;
-      // 64 columns per round: two back-to-back TMEM loads, one wait; the TMEM stage is handed back
-      // after the last round's loads, before that round is converted and stored
+      // 64 columns per round: two back-to-back TMEM loads, one wait. Accumulator 0 shares its last 64
+      // columns with accumulator 1's first 64, so the rounds of accumulator 0 run backwards: the shared
+      // columns are read first and the MMA issuer is told before they are converted and stored.
 #pragma unroll
-      for (int round = 0; round < C::EPI_COLS / 64; ++round) {
+      for (int i = 0; i < C::EPI_ROUNDS; ++i) {
+        const int round = a == 0 ? C::EPI_ROUNDS - 1 - i : i;
         uint32_t r[2][32];
         tw::tmem_load_32x32(t_base + round * 64, r[0]);
         tw::tmem_load_32x32(t_base + round * 64 + 32, r[1]);
         tw::tmem_load_wait();
-        if (round == C::EPI_COLS / 64 - 1) {
+        if (i == 0) {
           tw::tc_fence_before();
           __syncwarp();
-          if (lane == 0) tw::mbar_arrive(accEmpty + stage);
+          if (lane == 0) tw::mbar_arrive(sharedFree);
         }
         if (store) {
 #pragma unroll
