@@ -324,8 +324,9 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
       const uint32_t idesc_base = n_rows == BN ? IDESC_FULL : IDESC_128;
       ok = tw::mbar_wait_all(tabFull + tsl, tph, abort_flag);
       // the previous tile's epilogue has read the columns this accumulator shares with its own
+      // (its tcgen05.ld have completed - tcgen05.wait::ld - before it arrives on the barrier, so the MMAs
+      // issued below cannot overtake them)
       if (ok && it > 0) ok = tw::mbar_wait_all(sharedFree, (it - 1) & 1, abort_flag);
-      tw::tc_fence_after();
       const uint32_t acc = tmem + (it & 1) * C::ACC_STRIDE;
       uint32_t abits = 0, wbits[C::HALVES] = {};
       for (int st = 0; st < steps && ok; ++st) {
