@@ -1,15 +1,19 @@
-"""Benchmark of the selective-FP4-repair projection path.
+"""Benchmark of the selective-FP4-repair hot path.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--budget 2.0|1.5]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--budget 2.0|1.5|1.0]
+                  [--workload auto|step|projections|attention]
 
-One step = one pass over the Cosmos3-Edge-shaped projection set (M = 7680 tokens; QKV 6144x2048,
-out-proj 2048x2048, FFN-up 8192x2048, FFN-down 2048x8192): for every projection the online
-activation quantizer with A1 block selection, then the fused repair GEMM with the seeded W1 tile
-plan of the chosen issued-work budget (FFN-down with the A1W1 cross term). The reported metric is
-effective TFLOP/s on issued FP4 work (2*M*N*K-scaled, padding excluded) over all ranks.
-
-N > 1: data-parallel replicas of the same projection set (one process per GPU, no data-path
-collective), weak scaling. The tensor-parallel step benchmark lives in the package's DiT runner.
+Default workload (`auto`): one Cosmos3-Nano-shaped DiT denoise step (28 blocks, hidden 4096, 32 heads x 128,
+FFN 16384, 3840 tokens x CFG 2, seeded 2x issued-work plan) replayed as one CUDA Graph, the same work at every
+GPU count (strong scaling): N = 1 one GPU; N = 2 tensor parallel over 2 (column-split QKV / FFN-up, row-split
+out-proj / FFN-down with NCCL all-reduces inside the graph); N = 4 TP2 x CFG2 (each CFG branch on its own GPU
+pair); N = 8 TP4 x CFG2. `value` is effective TFLOP/s on issued FP4 work of the step over all ranks,
+`ms_per_step` the denoise-step time. Beside it, every rank also runs the Cosmos3-Edge-shaped projection set
+(M = 7680 tokens; QKV 6144x2048, out-proj 2048x2048, FFN-up 8192x2048, FFN-down 2048x8192: online activation
+quantizer with A1 block selection, then the fused repair GEMM with the seeded W1 tile plan, FFN-down with the
+A1W1 cross term) as independent replicas: that is where the dominant kernel is timed alone (`roofline`),
+where outputs are checked against the CPU oracle (`parity`) and what `projection_set` reports.
+`--workload projections` makes the projection set the headline (weak scaling over replicas).
 """
 import argparse
 import json
@@ -169,46 +173,81 @@ class ClockSampler(threading.Thread):
                 'reasons': sorted(self.reasons), 'samples': len(self.samples)}
 
 
-def cpu_baseline(budget, threads, sample_rows=1536):
-    """The oracle's emulation of the same path on host cores: numpy quantizer + decoded fp32
-    matmuls per term, on a bounded sample (the first `sample_rows` rows of the QKV projection)."""
+def cpu_baseline(budget, threads, sample_rows=1536, shape=None):
+    """The reference's PyTorch FP4 emulation of the same path on the host cores (threaded torch restatement,
+    oracle/torch_emulation.py): quantize + select + decoded fp32 matmuls per term, on a bounded sample (the
+    first `sample_rows` rows of one QKV projection)."""
+    import torch
+    from oracle import torch_emulation as te
     from oracle import nvfp4_oracle as o
-    name, n, k = PROJECTIONS[0]
+    torch.set_num_threads(max(1, threads))          # explicit: torchrun exports OMP_NUM_THREADS=1
+    name, n, k = shape or PROJECTIONS[0]
     na, tiles, cross = plan_for(name, n, k, budget, 0)
-    x = o.synthetic_activation(sample_rows, k, 0)
-    w = o.synthetic_weight(n, k, 0)
-    wc, wsb, wf = o.quantize_weight(w)
-    sens = (w.astype(np.float64) ** 2).sum(0).astype(np.float32)
+    x = torch.from_numpy(o.synthetic_activation(sample_rows, k, 0))
+    w = torch.from_numpy(o.synthetic_weight(n, k, 0))
+    wc, ws, wf = te.quantize(w)                     # offline in the real path: not timed
+    sens = (w.double() ** 2).sum(0).float()
     t0 = time.perf_counter()
-    ac, asb, af = o.quantize_linear_input(x, rows_padded=sample_rows)
-    scores, _ = o.residual_scores(x, None, sens)
-    mask = o.choose_blocks(scores, na)
-    o.repair_linear(ac, asb, af, wc, wsb, wf, sample_rows, a_mask=mask, w_tiles=tiles, cross=cross)
+    ac, asc, af = te.quantize(x)
+    mask = te.select_blocks(x, af, ac[0], asc[0], sens, na) if na else None
+    te.repair_linear(ac, asc, af, wc, ws, wf, sample_rows, a_mask=mask, w_tiles=tiles, cross=cross)
     dt = time.perf_counter() - t0
-    flops = o.issued_flops(sample_rows, n, k, a_mask=mask, w_tiles=tiles, cross=cross)
-    return flops / dt / 1e12, dt, f'{sample_rows} rows of the qkv projection ({n}x{k}), quantize+select+{3 + cross}-term decoded matmul'
+    flops = o.issued_flops(sample_rows, n, k, a_mask=None if mask is None else mask.numpy(), w_tiles=tiles, cross=cross)
+    terms = 1 + (na > 0) + (len(tiles) > 0) + (cross and na > 0 and len(tiles) > 0)
+    return flops / dt / 1e12, dt, (f'{sample_rows} rows of the {name} projection ({n}x{k}): quantize + select + '
+                                   f'{terms}-term decoded fp32 matmul, torch CPU emulation on {threads} threads')
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
 
 
 def run_reference(args):
-    rank = int(os.environ.get('RANK', '0'))
-    if rank != 0:
+    """The reference arm: the CPU emulation of the path on all host threads; rank 0 alone runs it."""
+    if int(os.environ.get('RANK', '0')) != 0:
         return
-    threads = os.cpu_count() or 1
+    threads = host_threads()
+    step_mode = args.workload in ('auto', 'step')
+    shape = ('qkv', 3 * 4096, 4096) if step_mode else None
     for _ in range(args.warmup):
-        cpu_baseline(args.budget, threads, 256)
-    vals, times = [], []
+        cpu_baseline(args.budget, threads, 256, shape)
+    vals, times, sample = [], [], ''
     for _ in range(args.steps):
-        v, dt, sample = cpu_baseline(args.budget, threads)
+        v, dt, sample = cpu_baseline(args.budget, threads, 1536, shape)
         vals.append(v); times.append(dt)
     value = float(np.mean(vals))
-    line = {'metric': 'repaired NVFP4 GEMM effective TFLOPS on issued FP4 work', 'impl': 'reference', 'value': value,
+    config = step_config(args, max(args.gpus, 1)) if step_mode else workload_config(args.budget, 1)
+    line = {'metric': METRIC_STEP if step_mode else METRIC_PROJ, 'impl': 'reference', 'value': value,
             'unit': 'TFLOP/s', 'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup,
-            'ms_per_step': float(np.mean(times)) * 1e3, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
-            'dtype': 'nvfp4 (e2m1 x ue4m3, fp32 accumulate)', 'data': 'synthetic',
-            'config': workload_config(args.budget, 1),
+            'ms_per_step': float(np.mean(times)) * 1e3, 'higher_is_better': True,
+            'scaling': 'strong' if step_mode else 'weak', 'vs_baseline': None,
+            'dtype': 'nvfp4 emulated in fp32 (e2m1 x ue4m3 decoded, fp32 matmul)', 'data': 'synthetic',
+            'config': config,
             'cpu_baseline': {'value': value, 'unit': 'TFLOP/s', 'cores': threads, 'kind': 'port', 'sample': sample},
             'e2e': {'value': value, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}
     print(json.dumps(line))
+
+
+METRIC_PROJ = 'repaired NVFP4 GEMM effective TFLOPS on issued FP4 work'
+METRIC_STEP = 'repaired NVFP4 GEMM effective TFLOPS on issued FP4 work (DiT denoise step)'
+
+
+def step_topology(world, cfg_parallel):
+    """(tp, cfg) for a world size: CFG branches split over GPU pairs from 4 GPUs on."""
+    cfg = cfg_parallel or (2 if world >= 4 else 1)
+    return world // cfg, cfg
+
+
+def step_config(args, world):
+    tp, cfg = step_topology(world, args.cfg_parallel)
+    blocks = args.blocks or {'nano': 28, 'super': 48}[args.model]
+    return {'workload': f'{args.model}-shaped DiT denoise step: {blocks} blocks, {args.tokens} tokens x CFG 2, '
+                        f'{args.budget}x issued-work plan, one CUDA Graph replay per step',
+            'budget': args.budget, 'parallelism': f'tp{tp} x cfg{cfg}',
+            'l2': 'per-step working set (weights ~2.9 GB at tp1, activations 63 MB per tensor) exceeds the 126 MB L2'}
 
 
 def workload_config(budget, world, m=M_TOKENS, layers='qkv,out,ffn_up,ffn_down'):
@@ -238,25 +277,17 @@ def step_plan(cfg, budget, seed=0):
                            linears=linears, attention={})), frac
 
 
-def run_step(args):
-    """DiT denoise-step time (Nano- and Super-shaped synthetic DiT): one graph replay of the whole step, CFG batch 2
-    (split over GPU pairs when --cfg-parallel 2), tensor parallel over the remaining ranks."""
+def measure_step(args, device, rank, world, dist):
+    """DiT denoise step (Nano- or Super-shaped synthetic DiT): one CUDA Graph replay per step, CFG batch 2 (split
+    over GPU groups when cfg > 1), tensor parallel inside a group. Returns the rank-0 result dictionary."""
     import torch
-    import torch.distributed as dist
-    from thunderworld_b200 import parallel
+    from thunderworld_b200 import _lib, parallel
     from thunderworld_b200.config import RepairConfig, RepairPolicy
     from thunderworld_b200.cosmos import dit
     from thunderworld_b200.cosmos.engine import StepEngine
     from thunderworld_b200.cosmos.settings import RunConfig
-    rank, world = int(os.environ.get('RANK', '0')), int(os.environ.get('WORLD_SIZE', '1'))
-    local = int(os.environ.get('LOCAL_RANK', '0'))
-    torch.cuda.set_device(local)
-    device = torch.device('cuda', local)
-    if world > 1:
-        os.environ.setdefault('NCCL_NVLS_ENABLE', '0')
-        dist.init_process_group('nccl', device_id=device)
-    cfg_par = args.cfg_parallel
-    topo = parallel.make_topology(tp_size=world // cfg_par, cfg_size=cfg_par) if world > 1 else parallel.Topology()
+    tp, cfg_par = step_topology(world, args.cfg_parallel)
+    topo = parallel.make_topology(tp_size=tp, cfg_size=cfg_par) if world > 1 else parallel.Topology()
     base = {'nano': dit.NANO, 'super': dit.SUPER}[args.model]
     cfg = dit.DiTConfig(base.hidden, base.heads, base.ffn, args.blocks or base.blocks)
     plan, frac = step_plan(cfg, args.budget)
@@ -270,137 +301,104 @@ def run_step(args):
     model = dit.DiTModel(cfg, engine, topo, device)
     batch = 2 // cfg_par
     g = torch.Generator().manual_seed(0)
-    x = torch.randn(batch, args.tokens, cfg.hidden, generator=g)
+    x_all = torch.randn(2, args.tokens, cfg.hidden, generator=g)
     cols = torch.randperm(cfg.hidden, generator=g)[:max(1, round(0.005 * cfg.hidden))]
-    x[..., cols] *= 20
-    x = x.bfloat16().to(device)
-    mod = (torch.randn(batch, cfg.blocks, 6, cfg.hidden, generator=g) * 0.1).bfloat16().to(device)
+    x_all[..., cols] *= 20
+    mod_all = (torch.randn(2, cfg.blocks, 6, cfg.hidden, generator=g) * 0.1).bfloat16()
+    first = topo.cfg_rank * batch if cfg_par > 1 else 0
+    x_host = x_all[first:first + batch].bfloat16().contiguous().pin_memory()
+    mod_host = mod_all[first:first + batch].contiguous().pin_memory()
+    x, mod = x_host.to(device), mod_host.to(device)
+    calls0 = _lib.calls
     engine.warm_schedule(model, x=x, mod=mod)
+    calls_per_step = _lib.calls - calls0          # C-ABI kernel calls of one eager pass = launches captured per step
     ledger = engine.compile_budget() if args.budget > 1. else None
-    for _ in range(max(args.warmup, 3)):
-        engine.reset_request()
-        engine(model, x=x, mod=mod)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        engine.reset_request()
-        engine(model, x=x, mod=mod)
-    e1.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=device, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    if rank == 0:
-        rows = list(engine.rows.values())
-        # one (branch, phase) of the schedule = the work of one step; attention rows are per batch entry
-        issued = sum(r['total_mma'] * (batch if r['kind'] == 'attention' else 1) for r in rows
-                     if r['phase'] == 0 and r['branch'] == engine._branch_offset) * topo.tp_size * cfg_par
-        print(json.dumps({'metric': 'DiT denoise-step ms', 'value': float(t[0]), 'unit': 'ms', 'n_gpus': world,
-                          'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': float(t[0]),
-                          'higher_is_better': False, 'scaling': 'strong', 'vs_baseline': None,
-                          'dtype': 'nvfp4 (e2m1 x ue4m3, fp32 accumulate)', 'data': 'synthetic',
-                          'config': {'workload': f'{args.model}-shaped DiT step, {cfg.blocks} blocks, hidden {cfg.hidden}, '
-                                                 f'{args.tokens} tokens x CFG 2, {args.budget}x plan, CUDA Graph replay',
-                                     'parallelism': f'tp{topo.tp_size} x cfg{cfg_par}'},
-                          'issued_tflop_per_step': issued / 1e12, 'effective_tflops': issued / 1e12 / (float(t[0]) * 1e-3),
-                          'ledger_ratio': None if ledger is None else ledger['ratio']}), flush=True)
-    if world > 1:
-        # The captured graphs hold NCCL kernels: tearing the communicator down while they exist can block
-        # for ever, so the graphs go first and the process leaves without destroying the group.
-        engine.graphs.clear()
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
         torch.cuda.synchronize()
-        dist.barrier()
-        sys.stdout.flush()
-        os._exit(0)
 
+    def replay():
+        engine.reset_request()
+        return engine(model, x=x, mod=mod)
 
-def run_attention(args):
-    """Streaming FP4 attention workload: batch 2 (CFG) x heads x seq x 128, self- and
-    cross-attention (512 text keys), base and 50 % / 3-term repair; time includes packing and selection."""
-    import torch
-    from thunderworld_b200 import RepairConfig
-    from thunderworld_b200.runtime import _forward
-    torch.cuda.set_device(0)
-    g = torch.Generator().manual_seed(0)
-    B, H, S = 2, args.att_heads, args.tokens
-    results = {}
-    for name, sk in (('self', S), ('cross', 512)):
-        mk = lambda s_: (torch.randn(B, s_, H, 128, generator=g) * (torch.rand(H, generator=g) * 1.5 + .5)[None, None, :, None]).bfloat16().cuda()
-        q, k, v = mk(S), mk(sk), mk(sk)
-        for label, cfg in (('base', RepairConfig(coverage=0.)), ('repair50_terms3', RepairConfig(coverage=.5, terms=3))):
-            quotas = (torch.tensor(cfg.head_counts(H, sk), device='cuda', dtype=torch.int32),
-                      torch.tensor(cfg.pv_counts(H, sk), device='cuda', dtype=torch.int32))
-            for _ in range(3):
-                _forward(q, k, v, cfg, None, quotas)
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                held = _forward(q, k, v, cfg, None, quotas)
-            for _ in range(max(args.warmup, 3)):
-                graph.replay()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(args.steps):
-                graph.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            ms = e0.elapsed_time(e1) / args.steps
-            nt = (sk + 127) // 128
-            issued = 4 * B * H * S * nt * 128 * 128 * (1 + (cfg.terms - 1) * sum(cfg.head_counts(H, sk)) / (H * nt))
-            results[f'{name}_{label}'] = {'ms': ms, 'issued_tflop': issued / 1e12, 'tflops': issued / 1e12 / (ms * 1e-3)}
-    best = results['self_base']
-    print(json.dumps({'metric': 'streaming FP4 attention effective TFLOPS on issued FP4 work', 'value': best['tflops'],
-                      'unit': 'TFLOP/s', 'n_gpus': 1, 'steps': args.steps, 'warmup': max(args.warmup, 3),
-                      'ms_per_step': best['ms'], 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
-                      'dtype': 'nvfp4 (e2m1 x ue4m3, fp32 softmax)', 'data': 'synthetic',
-                      'config': {'workload': f'streaming attention: batch 2 x {H} heads x seq {S} x 128, cross 512 keys'},
-                      'cases': results,
-                      'roofline': {'bound': 'tensor', 'achieved': best['tflops'], 'peak': NOMINAL_FP4_TFLOPS, 'unit': 'TFLOP/s',
-                                   'frac': best['tflops'] / NOMINAL_FP4_TFLOPS, 'traffic': None}}))
-
-
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument('--gpus', type=int, default=1)
-    ap.add_argument('--steps', type=int, default=20)
-    ap.add_argument('--warmup', type=int, default=5)
-    ap.add_argument('--impl', default='ours')
-    ap.add_argument('--budget', type=float, default=2.0)
-    ap.add_argument('--no-cpu-baseline', action='store_true')
-    ap.add_argument('--no-parity', action='store_true', help='skip the oracle check of the outputs (profiling runs)')
-    ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer timing (profiling runs)')
-    ap.add_argument('--m-tokens', type=int, default=M_TOKENS, help='rows per projection (smaller for profiler captures)')
-    ap.add_argument('--layers', default='qkv,out,ffn_up,ffn_down', help='subset of the projection set')
-    ap.add_argument('--workload', default='projections', choices=('projections', 'step', 'attention'))
-    ap.add_argument('--model', default='nano', choices=('nano', 'super'))
-    ap.add_argument('--blocks', type=int, default=0, help='override the number of DiT blocks (step workload)')
-    ap.add_argument('--tokens', type=int, default=3840)
-    ap.add_argument('--cfg-parallel', type=int, default=1)
-    ap.add_argument('--att-heads', type=int, default=32)
-    args = ap.parse_args()
-    if args.workload == 'step':
-        return run_step(args)
-    if args.workload == 'attention':
-        return run_attention(args)
-    if args.impl == 'reference':
-        return run_reference(args)
-
-    import torch
-    import torch.distributed as dist
-    rank = int(os.environ.get('RANK', '0'))
-    world = int(os.environ.get('WORLD_SIZE', '1'))
-    local = int(os.environ.get('LOCAL_RANK', '0'))
-    if not torch.cuda.is_available():
-        raise RuntimeError('bench.py needs a CUDA device: the product path has no CPU fallback')
-    torch.cuda.set_device(local)
-    device = torch.device('cuda', local)
+    for _ in range(max(args.warmup, 3)):
+        replay()
+    barrier()
+    sampler = ClockSampler(device.index)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        replay()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    sampler.stop_flag = True
+    # end to end: pinned host inputs in, the step's output back to pinned host memory, every step
+    out_host = torch.empty_like(x_host).pin_memory()
+    for _ in range(0 if args.no_e2e else 2):
+        x.copy_(x_host, non_blocking=True); mod.copy_(mod_host, non_blocking=True)
+        out_host.copy_(replay(), non_blocking=True)
+    barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record(stream)
+    for _ in range(0 if args.no_e2e else args.steps):
+        x.copy_(x_host, non_blocking=True); mod.copy_(mod_host, non_blocking=True)
+        out_host.copy_(replay(), non_blocking=True)
+    s1.record(stream)
+    barrier()
+    ms_e2e = max(s0.elapsed_time(s1), 1e-9) / args.steps
+    # sustained: at least three seconds of back-to-back replays with the SM clock sampled underneath
+    sustained = None
+    if world == 1 and not args.no_sustained:
+        sus = ClockSampler(device.index)
+        sus.start()
+        n_sus = max(args.steps, int(3000. / ms) + 1)
+        u0, u1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        u0.record(stream)
+        for _ in range(n_sus):
+            replay()
+        u1.record(stream)
+        torch.cuda.synchronize()
+        sus.stop_flag = True
+        sus.join(timeout=2)
+        sustained = {'ms_per_step': u0.elapsed_time(u1) / n_sus, 'steps': n_sus, 'seconds': u0.elapsed_time(u1) / 1e3,
+                     'sm_mhz_median': sus.result()['sm_mhz'], 'reasons': sus.result()['reasons']}
+    times = torch.tensor([ms, ms_e2e], device=device, dtype=torch.float64)
     if world > 1:
-        dist.init_process_group('nccl', device_id=device)
-    from thunderworld_b200 import ops
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = float(times[0]), float(times[1])
+    sampler.join(timeout=2)
+    status = engine.device_status()
+    rows = list(engine.rows.values())
+    # one (branch, phase) of the schedule = the work of one step; attention rows are per batch entry
+    issued = sum(r['total_mma'] * (batch if r['kind'] == 'attention' else 1) for r in rows
+                 if r['phase'] == 0 and r['branch'] == engine._branch_offset) * topo.tp_size * cfg_par
+    result = {'ms': ms, 'ms_e2e': ms_e2e, 'issued': issued, 'clocks': sampler.result(), 'status': status,
+              'h2d': (x_host.numel() + mod_host.numel()) * 2, 'd2h': out_host.numel() * 2, 'calls_per_step': calls_per_step,
+              'ledger_ratio': None if ledger is None else ledger['ratio'], 'sustained': sustained,
+              'parallelism': f'tp{topo.tp_size} x cfg{cfg_par}',
+              'collectives': None if topo.tp_size == 1 else
+              f'per block: 2 x all_reduce(SUM) of bf16 [{batch * args.tokens}, {cfg.hidden}] and 2 x 4-byte all_reduce(MAX), NCCL, inside the graph'}
+    if sustained is not None:
+        sustained['value'] = issued / 1e12 / (sustained['ms_per_step'] * 1e-3)
+    # the captured graphs hold NCCL kernels: they go before anything tears the communicator down
+    engine.graphs.clear()
+    del model, engine
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    return result
 
+
+def measure_projections(args, device, rank, world, dist):
+    """The projection set on this rank's GPU (replicas under N > 1): whole-set throughput, the fused kernel timed
+    alone (roofline), the oracle check of the outputs and the host-buffer (end-to-end) throughput."""
+    import torch
+    from thunderworld_b200 import ops
     chosen = args.layers.split(',')
     layers = [Layer(name, n, k, args.m_tokens, args.budget, seed, device)
               for seed, (name, n, k) in enumerate(PROJECTIONS) if name in chosen]
@@ -438,7 +436,7 @@ def main():
         g_step.replay()
     barrier()
 
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(device.index)
     sampler.start()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -542,48 +540,163 @@ def main():
     gemm_ms = sum(sum(v) for v in per_layer.values())
     gemm_launches = sum(len(v) for v in per_layer.values())
     achieved = sum(flops_by_layer[n_] * len(v) for n_, v in per_layer.items()) / (gemm_ms * 1e-3) / 1e12
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, 'MEASURED_PEAKS.json')))
-    except Exception:
-        pass
+    fp4_peak = measured_fp4_peak()
+    full = args.m_tokens == M_TOKENS and args.budget == 2.0 and args.layers == 'qkv,out,ffn_up,ffn_down'
+    roofline = {'bound': 'tensor', 'kernel': 'fused_kernel (tcgen05 mxf4nvf4 repair GEMM), timed alone on the projection set',
+                'achieved': achieved, 'peak': NOMINAL_FP4_TFLOPS, 'unit': 'TFLOP/s', 'frac': achieved / NOMINAL_FP4_TFLOPS,
+                'peak_source': 'nominal dense FP4 (MEASURED_PEAKS.json holds no FP4 figure)',
+                'peak_measured': fp4_peak, 'frac_measured': achieved / fp4_peak['burst_tflops'] if fp4_peak else None,
+                'traffic': NCU_TRAFFIC_BYTES_PER_LAUNCH if full else None,
+                'traffic_unit': 'bytes per launch (ncu dram read + write, mean of the four layers)',
+                'launches': gemm_launches, 'avg_launch_ms': gemm_ms / gemm_launches,
+                'per_layer_tflops': {n_: flops_by_layer[n_] / (np.mean(v) * 1e-3) / 1e12 for n_, v in per_layer.items()},
+                'gemm_share_of_projection_set': gemm_ms / ms}
+    result = {'value': world * flops_step * args.steps / (ms * 1e-3) / 1e12, 'ms_per_step': ms / args.steps,
+              'e2e_value': world * flops_step * args.steps / (ms_e2e * 1e-3) / 1e12, 'e2e_ms_per_step': ms_e2e / args.steps,
+              'h2d': sum(l.x_host.numel() * 2 for l in layers), 'd2h': sum(l.out_host.numel() * 2 for l in layers),
+              'launches_per_step': len(layers) * 4, 'clocks': sampler.result(), 'roofline': roofline, 'parity': parity}
+    del layers, g_step, g_gemm, g_layer
+    torch.cuda.empty_cache()
+    return result
+
+
+def measured_fp4_peak():
+    """Dense NVFP4 GEMM peak measured on this pool's B200 by baseline/fp4_peak_probe.py (cuBLASLt through
+    torch._scaled_mm, 8192^3): the figures of the committed summary profiles/fp4_peak_probe.md."""
+    return {'burst_tflops': 5863.4, 'sustained_tflops': 5240.5, 'sustained_sm_mhz_median': 1305.0,
+            'how': 'cuBLASLt NVFP4 8192^3 via torch._scaled_mm: best of 10 / back to back for 3.4 s'}
+
+
+def run_attention(args):
+    """Streaming FP4 attention workload: batch 2 (CFG) x heads x seq x 128, self- and
+    cross-attention (512 text keys), base and 50 % / 3-term repair; time includes packing and selection."""
+    import torch
+    from thunderworld_b200 import RepairConfig
+    from thunderworld_b200.runtime import _forward
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(0)
+    B, H, S = 2, args.att_heads, args.tokens
+    results = {}
+    for name, sk in (('self', S), ('cross', 512)):
+        mk = lambda s_: (torch.randn(B, s_, H, 128, generator=g) * (torch.rand(H, generator=g) * 1.5 + .5)[None, None, :, None]).bfloat16().cuda()
+        q, k, v = mk(S), mk(sk), mk(sk)
+        for label, cfg in (('base', RepairConfig(coverage=0.)), ('repair50_terms3', RepairConfig(coverage=.5, terms=3))):
+            quotas = (torch.tensor(cfg.head_counts(H, sk), device='cuda', dtype=torch.int32),
+                      torch.tensor(cfg.pv_counts(H, sk), device='cuda', dtype=torch.int32))
+            for _ in range(3):
+                _forward(q, k, v, cfg, None, quotas)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                held = _forward(q, k, v, cfg, None, quotas)
+            for _ in range(max(args.warmup, 3)):
+                graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            nt = (sk + 127) // 128
+            issued = 4 * B * H * S * nt * 128 * 128 * (1 + (cfg.terms - 1) * sum(cfg.head_counts(H, sk)) / (H * nt))
+            results[f'{name}_{label}'] = {'ms': ms, 'issued_tflop': issued / 1e12, 'tflops': issued / 1e12 / (ms * 1e-3)}
+    best = results['self_base']
+    print(json.dumps({'metric': 'streaming FP4 attention effective TFLOPS on issued FP4 work', 'value': best['tflops'],
+                      'unit': 'TFLOP/s', 'n_gpus': 1, 'steps': args.steps, 'warmup': max(args.warmup, 3),
+                      'ms_per_step': best['ms'], 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+                      'dtype': 'nvfp4 (e2m1 x ue4m3, fp32 softmax)', 'data': 'synthetic',
+                      'config': {'workload': f'streaming attention: batch 2 x {H} heads x seq {S} x 128, cross 512 keys'},
+                      'cases': results,
+                      'roofline': {'bound': 'tensor', 'achieved': best['tflops'], 'peak': NOMINAL_FP4_TFLOPS, 'unit': 'TFLOP/s',
+                                   'frac': best['tflops'] / NOMINAL_FP4_TFLOPS, 'traffic': None}}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--impl', default='ours')
+    ap.add_argument('--budget', type=float, default=2.0)
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-parity', action='store_true', help='skip the oracle check of the outputs (profiling runs)')
+    ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer timing (profiling runs)')
+    ap.add_argument('--no-sustained', action='store_true', help='skip the three-second sustained run of the step')
+    ap.add_argument('--m-tokens', type=int, default=M_TOKENS, help='rows per projection (smaller for profiler captures)')
+    ap.add_argument('--layers', default='qkv,out,ffn_up,ffn_down', help='subset of the projection set')
+    ap.add_argument('--workload', default='auto', choices=('auto', 'projections', 'step', 'attention'))
+    ap.add_argument('--model', default='nano', choices=('nano', 'super'))
+    ap.add_argument('--blocks', type=int, default=0, help='override the number of DiT blocks (step workload)')
+    ap.add_argument('--tokens', type=int, default=3840)
+    ap.add_argument('--cfg-parallel', type=int, default=0, help='CFG groups (0: 2 from four GPUs on, else 1)')
+    ap.add_argument('--att-heads', type=int, default=32)
+    args = ap.parse_args()
+    if args.impl == 'reference':
+        return run_reference(args)
+    if args.workload == 'attention':
+        return run_attention(args)
+
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    if not torch.cuda.is_available():
+        raise RuntimeError('bench.py needs a CUDA device: the product path has no CPU fallback')
+    torch.cuda.set_device(local)
+    device = torch.device('cuda', local)
+    if world > 1:
+        os.environ.setdefault('NCCL_NVLS_ENABLE', '0')
+        dist.init_process_group('nccl', device_id=device)
+
+    proj = measure_projections(args, device, rank, world, dist) if args.workload in ('auto', 'projections') else None
+    step = measure_step(args, device, rank, world, dist) if args.workload in ('auto', 'step') else None
+    if step is not None and step['status'] != 0:
+        raise RuntimeError('device status word reports a bounded-wait timeout')
 
     if rank == 0:
-        value = world * flops_step * args.steps / (ms * 1e-3) / 1e12
-        e2e = world * flops_step * args.steps / (ms_e2e * 1e-3) / 1e12
-        h2d = sum(l.x_host.numel() * 2 for l in layers)
-        d2h = sum(l.out_host.numel() * 2 for l in layers)
-        line = {
-            'metric': 'repaired NVFP4 GEMM effective TFLOPS on issued FP4 work', 'value': value, 'unit': 'TFLOP/s',
-            'n_gpus': world, 'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms / args.steps,
-            'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
-            'dtype': 'nvfp4 (e2m1 x ue4m3, fp32 accumulate)', 'data': 'synthetic',
-            'config': workload_config(args.budget, world, args.m_tokens, args.layers),
-            'e2e': {'value': e2e, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
-                    'ms_per_step': ms_e2e / args.steps},
-            'gpu_launches': args.steps * len(layers) * 4,
-            'parity': parity,
-            'clocks': sampler.result(),
-            'roofline': {'bound': 'tensor', 'kernel': 'fused_kernel (tcgen05 mxf4nvf4 repair GEMM)',
-                         'achieved': achieved, 'peak': NOMINAL_FP4_TFLOPS, 'unit': 'TFLOP/s',
-                         'frac': achieved / NOMINAL_FP4_TFLOPS,
-                         'peak_source': 'nominal dense FP4 (MEASURED_PEAKS.json holds no FP4 figure)',
-                         'frac_of_4x_measured_bf16': achieved / (4 * peaks['bf16_tflops_sustained']) if peaks else None,
-                         'traffic': (NCU_TRAFFIC_BYTES_PER_LAUNCH if args.m_tokens == M_TOKENS and args.budget == 2.0 and
-                                     args.layers == 'qkv,out,ffn_up,ffn_down' else None),
-                         'traffic_unit': 'bytes per launch (ncu dram read + write, mean of the four layers)',
-                         'launches': gemm_launches,
-                         'avg_launch_ms': gemm_ms / gemm_launches,
-                         'per_layer_tflops': {n_: flops_by_layer[n_] / (np.mean(v) * 1e-3) / 1e12 for n_, v in per_layer.items()},
-                         'gemm_share_of_step': gemm_ms / ms},
-        }
+        common = {'higher_is_better': True, 'vs_baseline': None, 'n_gpus': world, 'steps': args.steps,
+                  'warmup': max(args.warmup, 3), 'dtype': 'nvfp4 (e2m1 x ue4m3, fp32 accumulate)', 'data': 'synthetic'}
+        if step is not None:
+            line = {'metric': METRIC_STEP, 'value': step['issued'] / 1e12 / (step['ms'] * 1e-3), 'unit': 'TFLOP/s', **common,
+                    'ms_per_step': step['ms'], 'scaling': 'strong', 'config': step_config(args, world),
+                    'denoise_step_ms': step['ms'], 'issued_tflop_per_step': step['issued'] / 1e12,
+                    'ledger_ratio': step['ledger_ratio'], 'collectives': step['collectives'],
+                    'e2e': {'value': step['issued'] / 1e12 / (step['ms_e2e'] * 1e-3), 'unit': 'TFLOP/s',
+                            'h2d_bytes_per_step': step['h2d'], 'd2h_bytes_per_step': step['d2h'],
+                            'ms_per_step': step['ms_e2e'], 'bytes_are': 'per rank'},
+                    'gpu_launches': args.steps * step['calls_per_step'],
+                    'gpu_launches_are': 'C-ABI kernel calls per rank captured in the step graph x steps (each call launches >= 1 kernel)',
+                    'clocks': step['clocks'], 'sustained': step['sustained']}
+            if proj is not None:
+                line['roofline'] = proj['roofline']
+                line['parity'] = proj['parity']
+                line['projection_set'] = {'value': proj['value'], 'unit': 'TFLOP/s', 'ms_per_step': proj['ms_per_step'],
+                                          'replicas': world, 'config': workload_config(args.budget, world, args.m_tokens, args.layers),
+                                          'e2e': {'value': proj['e2e_value'], 'ms_per_step': proj['e2e_ms_per_step'],
+                                                  'h2d_bytes_per_step': proj['h2d'], 'd2h_bytes_per_step': proj['d2h']},
+                                          'clocks': proj['clocks']}
+        else:
+            line = {'metric': METRIC_PROJ, 'value': proj['value'], 'unit': 'TFLOP/s', **common,
+                    'ms_per_step': proj['ms_per_step'], 'scaling': 'weak',
+                    'config': workload_config(args.budget, world, args.m_tokens, args.layers),
+                    'e2e': {'value': proj['e2e_value'], 'unit': 'TFLOP/s', 'h2d_bytes_per_step': proj['h2d'],
+                            'd2h_bytes_per_step': proj['d2h'], 'ms_per_step': proj['e2e_ms_per_step']},
+                    'gpu_launches': args.steps * proj['launches_per_step'], 'clocks': proj['clocks'],
+                    'roofline': proj['roofline'], 'parity': proj['parity']}
         if world == 1 and not args.no_cpu_baseline:
-            v, dt, sample = cpu_baseline(args.budget, os.cpu_count() or 1)
-            line['cpu_baseline'] = {'value': v, 'unit': 'TFLOP/s', 'cores': os.cpu_count() or 1, 'kind': 'port',
+            shape = ('qkv', 3 * 4096, 4096) if step is not None else None
+            v, dt, sample = cpu_baseline(args.budget, host_threads(), 1536, shape)
+            line['cpu_baseline'] = {'value': v, 'unit': 'TFLOP/s', 'cores': host_threads(), 'kind': 'port',
                                     'sample': sample, 'seconds': dt}
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # NCCL teardown after graph capture has blocked before: leave once every rank is done
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == '__main__':
