@@ -417,44 +417,57 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   tw::reg_budget_shrink<ATT_REGS_CONTROL>();
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
-    if (lane == 0) {
+    // The whole warp walks the key tiles (warp-wide waits keep it converged); one elected lane issues the
+    // copies of a tile: issued from a single-lane branch the same instructions cost tens of cycles each.
+    {
       const int q_row = h * p.mp + mb * 128;
-      tw::mbar_expect_tx(qFull, (need_q1 ? 2u : 1u) * (ATT_TILE + ATT_SF));
-      tw::tma_load_2d(smem + L::OFF_Q, &tm_q, 0, q_row, qFull);
-      tw::bulk_load(smem + L::OFF_SFQ, p.sfq + ((size_t)h * p.mblk + mb) * ATT_SF, ATT_SF, qFull);
-      if (need_q1) {
-        tw::tma_load_2d(smem + L::OFF_Q + ATT_TILE, &tm_q, 0, p.hq * p.mp + q_row, qFull);
-        tw::bulk_load(smem + L::OFF_SFQ + ATT_SF, p.sfq + ((size_t)(p.hq + h) * p.mblk + mb) * ATT_SF, ATT_SF, qFull);
+      if (tw::elect_one()) {
+        tw::mbar_expect_tx(qFull, (need_q1 ? 2u : 1u) * (ATT_TILE + ATT_SF));
+        tw::tma_load_2d(smem + L::OFF_Q, &tm_q, 0, q_row, qFull);
+        tw::bulk_load(smem + L::OFF_SFQ, p.sfq + ((size_t)h * p.mblk + mb) * ATT_SF, ATT_SF, qFull);
+        if (need_q1) {
+          tw::tma_load_2d(smem + L::OFF_Q + ATT_TILE, &tm_q, 0, p.hq * p.mp + q_row, qFull);
+          tw::bulk_load(smem + L::OFF_SFQ + ATT_SF, p.sfq + ((size_t)(p.hq + h) * p.mblk + mb) * ATT_SF, ATT_SF, qFull);
+        }
       }
+      __syncwarp();
       bool ok = true;
       for (int t = 0; t < p.nt && ok; ++t) {
         const uint32_t s = t % ATT_SLOTS, ph = (t / ATT_SLOTS) & 1;
         const bool k1 = need_k1 && (sel[t] & 1), v1 = need_v1 && (sel[t] & 2);
-        ok = tw::mbar_wait(kEmpty + s, ph ^ 1, abort_flag);
+        ok = tw::mbar_wait_all(kEmpty + s, ph ^ 1, abort_flag);
         if (!ok) break;
-        tw::mbar_expect_tx(kFull + s, (k1 ? 2u : 1u) * (ATT_TILE + ATT_SF) + 512u);
-        tw::tma_load_2d(smem + L::OFF_K + s * 2 * ATT_TILE, &tm_k, 0, kh * p.np + t * 128, kFull + s);
-        tw::bulk_load(smem + L::OFF_SFK + s * 2 * ATT_SF, p.sfk + ((size_t)kh * p.nt + t) * ATT_SF, ATT_SF, kFull + s);
-        tw::bulk_load(smem + L::OFF_KF + s * 512, p.kf + (size_t)kh * p.np + t * 128, 512, kFull + s);
-        if (k1) {
-          tw::tma_load_2d(smem + L::OFF_K + (s * 2 + 1) * ATT_TILE, &tm_k, 0, (p.hk + kh) * p.np + t * 128, kFull + s);
-          tw::bulk_load(smem + L::OFF_SFK + (s * 2 + 1) * ATT_SF, p.sfk + ((size_t)(p.hk + kh) * p.nt + t) * ATT_SF, ATT_SF, kFull + s);
+        if (tw::elect_one()) {
+          tw::mbar_expect_tx(kFull + s, (k1 ? 2u : 1u) * (ATT_TILE + ATT_SF) + 512u);
+          tw::tma_load_2d(smem + L::OFF_K + s * 2 * ATT_TILE, &tm_k, 0, kh * p.np + t * 128, kFull + s);
+          tw::bulk_load(smem + L::OFF_SFK + s * 2 * ATT_SF, p.sfk + ((size_t)kh * p.nt + t) * ATT_SF, ATT_SF, kFull + s);
+          tw::bulk_load(smem + L::OFF_KF + s * 512, p.kf + (size_t)kh * p.np + t * 128, 512, kFull + s);
+          if (k1) {
+            tw::tma_load_2d(smem + L::OFF_K + (s * 2 + 1) * ATT_TILE, &tm_k, 0, (p.hk + kh) * p.np + t * 128, kFull + s);
+            tw::bulk_load(smem + L::OFF_SFK + (s * 2 + 1) * ATT_SF, p.sfk + ((size_t)(p.hk + kh) * p.nt + t) * ATT_SF, ATT_SF, kFull + s);
+          }
         }
-        ok = tw::mbar_wait(vEmpty + s, ph ^ 1, abort_flag);
+        __syncwarp();
+        ok = tw::mbar_wait_all(vEmpty + s, ph ^ 1, abort_flag);
         if (!ok) break;
-        tw::mbar_expect_tx(vFull + s, (v1 ? 2u : 1u) * (ATT_TILE + ATT_SF) + 512u);
-        tw::tma_load_2d(smem + L::OFF_V + s * 2 * ATT_TILE, &tm_v, 0, (kh * p.nt + t) * 128, vFull + s);
-        tw::bulk_load(smem + L::OFF_SFV + s * 2 * ATT_SF, p.sfv + ((size_t)kh * p.nt + t) * ATT_SF, ATT_SF, vFull + s);
-        tw::bulk_load(smem + L::OFF_VF + s * 512, p.vf + ((size_t)kh * p.nt + t) * 128, 512, vFull + s);
-        if (v1) {
-          tw::tma_load_2d(smem + L::OFF_V + (s * 2 + 1) * ATT_TILE, &tm_v, 0, ((p.hk + kh) * p.nt + t) * 128, vFull + s);
-          tw::bulk_load(smem + L::OFF_SFV + (s * 2 + 1) * ATT_SF, p.sfv + ((size_t)(p.hk + kh) * p.nt + t) * ATT_SF, ATT_SF, vFull + s);
+        if (tw::elect_one()) {
+          tw::mbar_expect_tx(vFull + s, (v1 ? 2u : 1u) * (ATT_TILE + ATT_SF) + 512u);
+          tw::tma_load_2d(smem + L::OFF_V + s * 2 * ATT_TILE, &tm_v, 0, (kh * p.nt + t) * 128, vFull + s);
+          tw::bulk_load(smem + L::OFF_SFV + s * 2 * ATT_SF, p.sfv + ((size_t)kh * p.nt + t) * ATT_SF, ATT_SF, vFull + s);
+          tw::bulk_load(smem + L::OFF_VF + s * 512, p.vf + ((size_t)kh * p.nt + t) * 128, 512, vFull + s);
+          if (v1) {
+            tw::tma_load_2d(smem + L::OFF_V + (s * 2 + 1) * ATT_TILE, &tm_v, 0, ((p.hk + kh) * p.nt + t) * 128, vFull + s);
+            tw::bulk_load(smem + L::OFF_SFV + (s * 2 + 1) * ATT_SF, p.sfv + ((size_t)(p.hk + kh) * p.nt + t) * ATT_SF, ATT_SF, vFull + s);
+          }
         }
+        __syncwarp();
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // Whole, converged warp; one elected lane issues the tcgen05 operations of a product (scale copies, MMAs,
+    // commits) in one straight block.
+    {
       constexpr uint32_t IDESC = tw::make_idesc_nvf4(128, 128);
       constexpr uint64_t D64 = (uint64_t(1) << 46) | (uint64_t(4) << 61) | (uint64_t(512 >> 4) << 32) | (uint64_t(1) << 16);
       constexpr uint64_t DSF = (uint64_t(1) << 46) | (uint64_t(128 >> 4) << 32);
@@ -468,28 +481,34 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         tw::tc_mma_nvf4(tmem + d, D64 | lo(a_off), D64 | lo(b_off), IDESC, tmem + sfa, tmem + sfb, first ? 0u : 1u);
         tw::tc_mma_nvf4(tmem + d, D64 | lo(a_off + 32), D64 | lo(b_off + 32), IDESC, tmem + sfa + 4, tmem + sfb + 4, 1u);
       };
-      bool ok = tw::mbar_wait(qFull, 0, abort_flag);
+      bool ok = tw::mbar_wait_all(qFull, 0, abort_flag);
       tw::tc_fence_after();
-      copy_sf(TM_SFQ0, L::OFF_SFQ);
-      if (need_q1) copy_sf(TM_SFQ1, L::OFF_SFQ + ATT_SF);
+      if (tw::elect_one()) {
+        copy_sf(TM_SFQ0, L::OFF_SFQ);
+        if (need_q1) copy_sf(TM_SFQ1, L::OFF_SFQ + ATT_SF);
+      }
+      __syncwarp();
       // scores of key tile t into S[t & 1]
       auto issue_qk = [&](int t) {
         const uint32_t s = t % ATT_SLOTS, ph = (t / ATT_SLOTS) & 1, par = t & 1;
-        if (!tw::mbar_wait(kFull + s, ph, abort_flag) || !tw::mbar_wait(sEmpty + par, ((t >> 1) & 1) ^ 1, abort_flag)) return false;
+        if (!tw::mbar_wait_all(kFull + s, ph, abort_flag) || !tw::mbar_wait_all(sEmpty + par, ((t >> 1) & 1) ^ 1, abort_flag)) return false;
         tw::tc_fence_after();
         const bool rep = sel[t] & 1;
         const int k0 = L::OFF_K + s * 2 * ATT_TILE, k1 = k0 + ATT_TILE;
-        copy_sf(TM_SFK0 + par * 8, L::OFF_SFK + s * 2 * ATT_SF);
-        mma(TM_S + par * 128, L::OFF_Q, k0, TM_SFQ0, TM_SFK0 + par * 8, true);
-        if (rep) {
-          mma(TM_S + par * 128, L::OFF_Q + ATT_TILE, k0, TM_SFQ1, TM_SFK0 + par * 8, false);
-          if (p.terms >= 3) {
-            copy_sf(TM_SFK1 + par * 8, L::OFF_SFK + (s * 2 + 1) * ATT_SF);
-            mma(TM_S + par * 128, L::OFF_Q, k1, TM_SFQ0, TM_SFK1 + par * 8, false);
-            if (p.terms == 4) mma(TM_S + par * 128, L::OFF_Q + ATT_TILE, k1, TM_SFQ1, TM_SFK1 + par * 8, false);
+        if (tw::elect_one()) {
+          copy_sf(TM_SFK0 + par * 8, L::OFF_SFK + s * 2 * ATT_SF);
+          mma(TM_S + par * 128, L::OFF_Q, k0, TM_SFQ0, TM_SFK0 + par * 8, true);
+          if (rep) {
+            mma(TM_S + par * 128, L::OFF_Q + ATT_TILE, k0, TM_SFQ1, TM_SFK0 + par * 8, false);
+            if (p.terms >= 3) {
+              copy_sf(TM_SFK1 + par * 8, L::OFF_SFK + (s * 2 + 1) * ATT_SF);
+              mma(TM_S + par * 128, L::OFF_Q, k1, TM_SFQ0, TM_SFK1 + par * 8, false);
+              if (p.terms == 4) mma(TM_S + par * 128, L::OFF_Q + ATT_TILE, k1, TM_SFQ1, TM_SFK1 + par * 8, false);
+            }
           }
+          tw::tc_commit(sFull + par);        // (the K slot is released by the softmax group once it has read kf)
         }
-        tw::tc_commit(sFull + par);        // (the K slot is released by the softmax group once it has read kf)
+        __syncwarp();
         return true;
       };
       // S is double-buffered by tile parity = by softmax group. The scores of tile t + 2 are issued as soon as
@@ -504,26 +523,27 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const bool rep = sel[t] & 2;
         const int p0 = L::OFF_P + par * 2 * ATT_TILE, p1 = p0 + ATT_TILE;
         const int v0 = L::OFF_V + s * 2 * ATT_TILE, v1 = v0 + ATT_TILE;
-        // the V scale factors do not depend on P: copy them while the softmax group is still writing it
-        ok = tw::mbar_wait(vFull + s, ph, abort_flag);
-        if (!ok) break;
-        copy_sf(TM_SFV0 + par * 8, L::OFF_SFV + s * 2 * ATT_SF);
-        if (rep && p.pv_terms >= 3) copy_sf(TM_SFV1 + par * 8, L::OFF_SFV + (s * 2 + 1) * ATT_SF);
-        ok = tw::mbar_wait(pFull + par, (t >> 1) & 1, abort_flag) && tw::mbar_wait(tEmpty, (t & 1) ^ 1, abort_flag);
+        ok = tw::mbar_wait_all(vFull + s, ph, abort_flag) && tw::mbar_wait_all(pFull + par, (t >> 1) & 1, abort_flag) &&
+             tw::mbar_wait_all(tEmpty, (t & 1) ^ 1, abort_flag);
         if (!ok) break;
         tw::tc_fence_after();
-        copy_sf(TM_SFP0 + par * 8, L::OFF_SFP + par * 2 * ATT_SF);
-        mma(TM_T, p0, v0, TM_SFP0 + par * 8, TM_SFV0 + par * 8, true);
-        if (rep) {
-          copy_sf(TM_SFP1 + par * 8, L::OFF_SFP + (par * 2 + 1) * ATT_SF);
-          mma(TM_T, p1, v0, TM_SFP1 + par * 8, TM_SFV0 + par * 8, false);
-          if (p.pv_terms >= 3) {
-            mma(TM_T, p0, v1, TM_SFP0 + par * 8, TM_SFV1 + par * 8, false);
-            if (p.pv_terms == 4) mma(TM_T, p1, v1, TM_SFP1 + par * 8, TM_SFV1 + par * 8, false);
+        if (tw::elect_one()) {
+          copy_sf(TM_SFV0 + par * 8, L::OFF_SFV + s * 2 * ATT_SF);
+          if (rep && p.pv_terms >= 3) copy_sf(TM_SFV1 + par * 8, L::OFF_SFV + (s * 2 + 1) * ATT_SF);
+          copy_sf(TM_SFP0 + par * 8, L::OFF_SFP + par * 2 * ATT_SF);
+          mma(TM_T, p0, v0, TM_SFP0 + par * 8, TM_SFV0 + par * 8, true);
+          if (rep) {
+            copy_sf(TM_SFP1 + par * 8, L::OFF_SFP + (par * 2 + 1) * ATT_SF);
+            mma(TM_T, p1, v0, TM_SFP1 + par * 8, TM_SFV0 + par * 8, false);
+            if (p.pv_terms >= 3) {
+              mma(TM_T, p0, v1, TM_SFP0 + par * 8, TM_SFV1 + par * 8, false);
+              if (p.pv_terms == 4) mma(TM_T, p1, v1, TM_SFP1 + par * 8, TM_SFV1 + par * 8, false);
+            }
           }
+          tw::tc_commit(tFull);              // (the V slot is released by the accumulate warps once they have read vf)
+          tw::tc_commit(pEmpty + par);
         }
-        tw::tc_commit(tFull);              // (the V slot is released by the accumulate warps once they have read vf)
-        tw::tc_commit(pEmpty + par);
+        __syncwarp();
       }
     }
   }

@@ -75,7 +75,15 @@ __global__ void __launch_bounds__(256) amax_kernel(const uint4* __restrict__ x, 
   if (!PRESCALE) peak = fmaxf(__low2float(pk), __high2float(pk));
 #pragma unroll
   for (int o = 16; o; o >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, o));
-  if ((threadIdx.x & 31) == 0 && peak > 0.f) atomicMax(out, __float_as_uint(peak));
+  // one atomic per CTA: thousands of warps updating one word serialise in the L2
+  __shared__ float warp_peak[8];
+  if ((threadIdx.x & 31) == 0) warp_peak[threadIdx.x >> 5] = peak;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int w = 1; w < 8; ++w) peak = fmaxf(peak, warp_peak[w]);
+    if (peak > 0.f) atomicMax(out, __float_as_uint(peak));
+  }
 }
 
 // Correctly rounded a / b from r = RN(1 / b): q0 = RN(a r), e = a - b q0 (exact in an FMA),
