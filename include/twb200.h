@@ -100,6 +100,8 @@ typedef struct TwRepairIO {
                               FP4Linear kernel does (thunderworld_fp4/_linear_kernels.py:79-81) */
   int32_t mask_per_n;      /* nonzero: mask is bool [ceil(m/128), n/128, k/128], one A support per output
                               block (explicit masks of FP4Linear, thunderworld_fp4/linear.py:115-119) */
+  int32_t kernel;          /* 0: the library chooses (today: the single-CTA kernel); 1: single-CTA kernel; 2: CTA-pair kernel (cta_group::2;
+                              needs n % 256 == 0, m > 128 and no mask_per_n). Both give the same bits. */
 } TwRepairIO;
 /* Limits: n % 128 == 0, k % 128 == 0, k <= 24576 (else the "size exceeds the stated maximum" status).
  * Bytes of caller-owned workspace (holds the device status word; zero it once). */

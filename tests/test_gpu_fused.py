@@ -115,6 +115,39 @@ def test_projection_set_layers_at_benchmark_shape(index, budget):
     assert res['rel_l2'] <= TOL, res
 
 
+PAIR_CASES = [
+    (256, 256, 256, 0.0, 0.0, False),       # one pair tile, base only
+    (300, 512, 1024, 0.5, 0.5, True),       # three row blocks: the last pair's peer has no rows
+    (512, 1024, 2048, 0.25, 0.25, True),
+    (1024, 512, 768, 1.0, 0.0, False),      # full A1, odd number of K128 blocks
+    (640, 768, 512, 0.5, 1.0, True),        # dense W1 addressing
+    (130, 256, 24576, 0.25, 0.25, False),   # the largest supported K
+    (9728, 512, 256, 0.5, 0.5, False),      # more pair tiles than resident pairs
+]
+
+
+@pytest.mark.parametrize('m,n,k,af,wf,cross', PAIR_CASES)
+def test_pair_kernel_matches_single_cta_kernel_and_oracle(m, n, k, af, wf, cross):
+    """The CTA-pair kernel (tcgen05 cta_group::2) issues the same MMAs in the same order per output element as
+    the single-CTA kernel (the A1 blocks it adds for the union of two supports are zeros), so the two agree bit
+    for bit; both are within the tolerance of the oracle."""
+    from thunderworld_b200 import ops
+    op, x, weights, am, tiles = build(m, n, k, 23, af, wf, cross)
+    packed = op.pack(x)
+    op.kernel = 1
+    single = op.run_packed(x, packed)
+    op.kernel = 2
+    pair = op.run_packed(x, packed)
+    pair2 = op.run_packed(x, packed)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert torch.isfinite(pair.float()).all()
+    assert torch.equal(pair, pair2)
+    assert torch.equal(pair, single)
+    want = oracle_output(op, x, weights, packed, am, tiles, cross)
+    assert rel_l2(pair.float().cpu().numpy(), want) <= TOL
+
+
 def test_linearity_in_alpha_and_zero_activation():
     """Size-independent properties: zero input gives exact zeros; the output scales with alpha."""
     op, x, weights, am, tiles = build(256, 512, 512, 3, 0.5, 0.5, True)

@@ -15,7 +15,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / 'csrc'
 LIB = HERE / 'libtwb200.so'
 META = HERE / 'libtwb200.build.json'
-SOURCES = ('tw_api.cu', 'tw_quantize.cu', 'tw_fused.cu', 'tw_attention.cu', 'tw_pointwise.cu')
+SOURCES = ('tw_api.cu', 'tw_quantize.cu', 'tw_fused.cu', 'tw_fused_pair.cu', 'tw_attention.cu', 'tw_pointwise.cu')
 HEADERS = ('tw_common.cuh', '../../include/twb200.h')
 FLAGS = ['-std=c++17', '-O3', '-lineinfo', '-gencode', 'arch=compute_100a,code=sm_100a',
          '--shared', '-Xcompiler=-fPIC', '-Xptxas=-v']

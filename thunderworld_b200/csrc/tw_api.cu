@@ -19,4 +19,4 @@ extern "C" const char* tw_status(int status) {
   }
 }
 
-extern "C" int tw_abi_version(void) { return 1; }
+extern "C" int tw_abi_version(void) { return 2; }

@@ -1,6 +1,6 @@
 // Shared device helpers for the sm_100a kernels: NVFP4 number formats, mbarrier,
 // TMA (cp.async.bulk[.tensor]) and tcgen05 (tensor memory + block-scaled MMA)
-// wrappers written as inline PTX. No multicast forms are used anywhere.
+// wrappers written as inline PTX. Every load is a plain (single-destination) copy.
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
@@ -169,6 +169,17 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
       "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
       ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+
+// Tiled bulk store shared -> global (x = innermost coordinate; x * element size must be a multiple of 16 bytes;
+// parts of the box outside the tensor are not written). Joins the thread's current bulk group.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, const void* src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
+               "cp.async.bulk.commit_group;"
+               ::"l"(tmap), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
+// The issuing thread's bulk stores have finished reading shared memory / have completed.
+__device__ __forceinline__ void bulk_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------
 // tcgen05: tensor memory and block-scaled MMA (cta_group::1 only)

@@ -38,13 +38,13 @@ constexpr int KB_MAX = 192;               // K <= 24576
 constexpr int UNIT_TILE = 128 * 64;       // bytes of one 128-row x K128 code tile
 constexpr int SF_ATOM = 1024;             // bytes of the scales of 128 rows x K128
 
-// DEEP = true trades one base stage for deeper repair-unit rings (plans with W1 tiles and an A1 quota of at
-// least half the K blocks); without repair terms the third base stage is worth more. The host picks.
+// DEEP = true: the call issues repair terms; one base stage of the 256-wide tile is traded for the unit rings.
+// Without repair terms (plain W4A4) the rings shrink to one unused slot each and the third base stage stays.
 template <int BN, bool DEEP = false> struct Cfg {
   static constexpr int HALVES = BN / 128;
-  static constexpr int STAGES = BN == 256 ? (DEEP ? 2 : 3) : 4;   // base stages (K256 of A0 and W0)
-  static constexpr int A1_SLOTS = BN == 256 ? (DEEP ? 4 : 2) : 3;  // A1 units
-  static constexpr int W1_SLOTS = BN == 256 ? (DEEP ? 6 : 4) : 3;  // W1 units
+  static constexpr int STAGES = BN == 256 && DEEP ? 2 : 3;    // base stages (K256 of A0 and W0)
+  static constexpr int A1_SLOTS = DEEP ? 3 : 1;               // A1 units
+  static constexpr int W1_SLOTS = DEEP ? (BN == 256 ? 5 : 3) : 1;  // W1 units
   static constexpr int TAB_SLOTS = 3;                         // per-tile term tables built ahead
   static constexpr int EPI_WARPS = 8;
   static constexpr int FIRST_EPI_WARP = 8;                    // warps 0-3 and 6 are control roles, 4, 5, 7 idle
@@ -60,7 +60,9 @@ template <int BN, bool DEEP = false> struct Cfg {
   static constexpr int OFF_W0 = OFF_A0 + STAGES * A0_TILE;
   static constexpr int OFF_A1 = OFF_W0 + STAGES * W0_TILE;
   static constexpr int OFF_W1 = OFF_A1 + A1_SLOTS * UNIT_TILE;
-  static constexpr int OFF_SF0 = OFF_W1 + W1_SLOTS * UNIT_TILE;
+  static constexpr int EPI_BYTES = EPI_WARPS * 32 * 128;      // per epilogue warp: 32 rows x 64 bf16 columns, staged for a TMA store
+  static constexpr int OFF_EPI = OFF_W1 + W1_SLOTS * UNIT_TILE;
+  static constexpr int OFF_SF0 = OFF_EPI + EPI_BYTES;
   static constexpr int OFF_SFA1 = OFF_SF0 + STAGES * STAGE_SF;
   static constexpr int OFF_SFW1 = OFF_SFA1 + A1_SLOTS * SF_ATOM;
   static constexpr int OFF_TAB = OFF_SFW1 + W1_SLOTS * SF_ATOM;
@@ -79,9 +81,10 @@ template <int BN, bool DEEP = false> struct Cfg {
   static constexpr int TM_COLS = 512;
   static_assert(TM_SFW1 + 8 <= TM_COLS, "tensor memory budget");
   // a step is issued only when all its units have landed, so the rings must hold the units of one step
-  static_assert(A1_SLOTS >= 2 && W1_SLOTS >= 2 * HALVES, "unit rings hold at least one step");
+  static_assert(!DEEP || (A1_SLOTS >= 2 && W1_SLOTS >= 2 * HALVES), "unit rings hold at least one step");
 };
-static_assert(Cfg<256>::SMEM_BYTES <= 232448 && Cfg<256, true>::SMEM_BYTES <= 232448 && Cfg<128>::SMEM_BYTES <= 232448,
+static_assert(Cfg<256>::SMEM_BYTES <= 232448 && Cfg<256, true>::SMEM_BYTES <= 232448 && Cfg<128>::SMEM_BYTES <= 232448 &&
+              Cfg<128, true>::SMEM_BYTES <= 232448,
               "shared memory budget");
 
 struct Params {
@@ -150,7 +153,8 @@ __device__ __forceinline__ void build_table(TermTable<BN>& tab, const Params& p,
 template <int BN, bool DEEP>
 __global__ void __launch_bounds__(Cfg<BN, DEEP>::THREADS, 1)
 fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
-             const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1, const Params p) {
+             const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
+             const __grid_constant__ CUtensorMap tm_out, const Params p) {
   using C = Cfg<BN, DEEP>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -182,13 +186,17 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
     *abort_flag = 0;
     tw::fence_barrier_init();
     tw::tma_prefetch_desc(&tm_a0); tw::tma_prefetch_desc(&tm_a1);
-    tw::tma_prefetch_desc(&tm_w0); tw::tma_prefetch_desc(&tm_w1);
+    tw::tma_prefetch_desc(&tm_w0); tw::tma_prefetch_desc(&tm_w1); tw::tma_prefetch_desc(&tm_out);
   }
   if (warp == 1) { tw::tmem_alloc(tmem_slot, C::TM_COLS); tw::tmem_relinquish(); }
   tw::tc_fence_before();
   __syncthreads();
   tw::tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
+  // The kernel owns all 512 columns of the SM's tensor memory, so the allocation starts at lane 0, column 0;
+  // using the constant keeps every tensor-memory address of the MMA issuer a compile-time value. A different
+  // answer (it would mean another allocation is live on this SM) is reported, not ignored.
+  if (*tmem_slot != 0u) *abort_flag = 1;
+  constexpr uint32_t tmem = 0u;
 
   if (warp == 3) {
     // ------------------------------------------------------------------ term tables, built ahead
@@ -425,9 +433,16 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
     }
   } else if (warp >= C::FIRST_EPI_WARP) {
     // ------------------------------------------------------------------ epilogue
+    // TMEM -> registers -> bf16 -> this warp's staging tile in shared memory (32 rows x 128 bytes, 128-byte
+    // swizzle) -> one TMA store per 64 columns. Plain global stores of row-per-lane fragments touch 32 lines per
+    // instruction and held this SM's load/store pipe for thousands of cycles per tile, behind which the MMA
+    // issuer's own shared-memory and barrier operations queued; the bulk store leaves that pipe alone, writes
+    // whole lines and clips rows beyond M by itself.
     const int quad = warp & 3;                              // TMEM lane quadrant this warp may read
     const int group = (warp - C::FIRST_EPI_WARP) >> 2;      // column group
     const float alpha = __ldg(p.alpha);
+    uint8_t* stage = smem + C::OFF_EPI + (warp - C::FIRST_EPI_WARP) * 4096;
+    uint8_t* my_row = stage + lane * 128;
     uint32_t it = 0;
     for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++it) {
       const int mbi = tile / p.tiles_n, nt = tile % p.tiles_n;
@@ -435,14 +450,13 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
       if (!tw::mbar_wait_warp(accFull + a, (it >> 1) & 1, abort_flag)) break;
       tw::tc_fence_after();
       const uint32_t t_base = tmem + ((uint32_t)(quad * 32) << 16) + a * C::ACC_STRIDE + group * C::EPI_COLS;
-      const int row = mbi * 128 + quad * 32 + lane;
+      const int row0 = mbi * 128 + quad * 32;
       const int col = nt * BN + group * C::EPI_COLS;
-      __nv_bfloat16* dst = p.out + (size_t)row * p.n + col;
-      const bool store = row < p.m && col < p.n;
+      const bool live = col < p.n;                          // 128 columns of a 256-wide kernel never happen; kept for safety
       // 64 columns per round: two back-to-back TMEM loads, one wait. Accumulator 0 shares its last 64
       // columns with accumulator 1's first 64, so the rounds of accumulator 0 run backwards: the shared
       // columns are read first and the MMA issuer is told before they are converted and stored.
-#pragma unroll
+#pragma unroll 1
       for (int i = 0; i < C::EPI_ROUNDS; ++i) {
         const int round = a == 0 ? C::EPI_ROUNDS - 1 - i : i;
         uint32_t r[2][32];
@@ -454,37 +468,42 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
           __syncwarp();
           if (lane == 0) tw::mbar_arrive(sharedFree);
         }
-        if (store) {
+        // the previous store of this warp has finished reading the staging tile
+        if (lane == 0) tw::bulk_store_wait_read();
+        __syncwarp();
 #pragma unroll
-          for (int part = 0; part < 2; ++part) {
+        for (int part = 0; part < 2; ++part) {
 #pragma unroll
-            for (int v = 0; v < 2; ++v) {                   // 16 columns = 32 bytes per store
-              uint32_t w[8];
-              uint32_t bw[8] = {};
-              if (p.bias) {
-                const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col + round * 64 + part * 32 + v * 16);
-                const uint4 b0 = __ldg(bp), b1 = __ldg(bp + 1);
-                bw[0] = b0.x; bw[1] = b0.y; bw[2] = b0.z; bw[3] = b0.w; bw[4] = b1.x; bw[5] = b1.y; bw[6] = b1.z; bw[7] = b1.w;
-              }
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const float lo = __fmaf_rn(__uint_as_float(r[part][16 * v + 2 * q]), alpha, tw::bf16_bits_to_float(bw[q] & 0xffffu));
-                const float hi = __fmaf_rn(__uint_as_float(r[part][16 * v + 2 * q + 1]), alpha, tw::bf16_bits_to_float(bw[q] >> 16));
-                __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
-                w[q] = *reinterpret_cast<uint32_t*>(&b2);
-              }
-              tw::store_256(dst + round * 64 + part * 32 + v * 16, w);
+          for (int v = 0; v < 4; ++v) {                     // 8 columns = 16 bytes per shared-memory store
+            uint32_t bw[4] = {};
+            if (p.bias) {
+              const uint4 b0 = __ldg(reinterpret_cast<const uint4*>(p.bias + col + round * 64 + part * 32 + v * 8));
+              bw[0] = b0.x; bw[1] = b0.y; bw[2] = b0.z; bw[3] = b0.w;
             }
+            uint32_t w[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float lo = __fmaf_rn(__uint_as_float(r[part][8 * v + 2 * q]), alpha, tw::bf16_bits_to_float(bw[q] & 0xffffu));
+              const float hi = __fmaf_rn(__uint_as_float(r[part][8 * v + 2 * q + 1]), alpha, tw::bf16_bits_to_float(bw[q] >> 16));
+              __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
+              w[q] = *reinterpret_cast<uint32_t*>(&b2);
+            }
+            const int chunk = part * 4 + v;                 // 16-byte chunk of the 128-byte row; swizzled by the row
+            *reinterpret_cast<uint4*>(my_row + ((chunk ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
+        tw::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0 && live) tw::tma_store_2d(&tm_out, stage, col + round * 64, row0);
       }
     }
+    if (lane == 0) tw::bulk_store_wait_all();               // global writes are complete before the CTA exits
   }
 
   tw::tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, TW_ERR_TIMEOUT);
-  if (warp == 1) { tw::tc_fence_after(); tw::tmem_dealloc(tmem, C::TM_COLS); }
+  if (warp == 1) { tw::tc_fence_after(); tw::tmem_dealloc(*tmem_slot, C::TM_COLS); }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -542,6 +561,16 @@ int launch(int m, int n, int k, const void* a_codes, const void* w_codes, const 
     if (!make_map(&tm_w1, 2, has ? (const void*)io->wr : w_codes, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B))
       return TW_ERR_TENSOR_MAP;
   }
+  CUtensorMap tm_out;
+  {
+    // output bf16 [m, n]: boxes of 64 columns x 32 rows (one epilogue warp's staging tile); rows >= m are clipped
+    cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)m};
+    cuuint64_t strides[1] = {(cuuint64_t)n * 2};
+    cuuint32_t box[2] = {64, 32}, ones[2] = {1, 1};
+    if (encode_fn()(&tm_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return TW_ERR_TENSOR_MAP;
+  }
   Params p{};
   p.sfa0 = static_cast<const uint8_t*>(sfa);
   p.sfa1 = io->a1s_swz;
@@ -564,11 +593,15 @@ int launch(int m, int n, int k, const void* a_codes, const void* w_codes, const 
     configured[dev].store(true, std::memory_order_release);
   }
   const int grid = p.tiles < sms ? p.tiles : sms;
-  fused_kernel<BN, DEEP><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tm_a0, tm_a1, tm_w0, tm_w1, p);
+  fused_kernel<BN, DEEP><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tm_a0, tm_a1, tm_w0, tm_w1, tm_out, p);
   return cudaGetLastError() == cudaSuccess ? TW_OK : TW_ERR_LAUNCH;
 }
 
 }  // namespace
+
+int tw_fused_pair_launch(int m, int n, int k, const void* a_codes, const void* w_codes, const void* sfa, const void* sfb,
+                         void* out, const float* alpha, void* workspace, cudaStream_t stream, const TwRepairIO* io,
+                         int sms, int dev);                              // tw_fused_pair.cu
 
 extern "C" size_t tw_workspace(int, int, int) { return 256; }
 
@@ -602,11 +635,19 @@ extern "C" int tw_fused(int m, int n, int k, const void* a_codes, const void* w_
   cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
   if (major != 10) return TW_ERR_ARCH;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (io->kernel < 0 || io->kernel > 2) return TW_ERR_ARGUMENT;
+  // 256-wide tiles on CTA pairs (two row blocks per tile) unless the caller asks for the single-CTA kernel
+  const bool pair_ok = n % 256 == 0 && !io->mask_per_n && m > 128;
+  if (io->kernel == 2 && !pair_ok) return TW_ERR_SHAPE;
+  // (measured on B200: the pair kernel does not beat the single-CTA kernel - both are bound by the rate at which
+  // one thread can issue tcgen05 operations, and a pair has one issuing thread for two SMs - so it runs on request)
+  if (pair_ok && io->kernel == 2)
+    return tw_fused_pair_launch(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms, dev);
+  const bool repair = io->na > 0 || io->hasw;
   if (n % 256 == 0 && !io->mask_per_n) {
-    // with W1 tiles and an A1 quota of at least half the K blocks the unit rings are the scarcer resource
-    // (2x plan: +1 %), below that the third base stage is (1.5x plan: +1.3 %, base plan: +16 %)
-    if (io->hasw && 2 * io->na >= k / 128) return launch<256, true>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms, dev);
+    if (repair) return launch<256, true>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms, dev);
     return launch<256, false>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms, dev);
   }
+  if (repair) return launch<128, true>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms, dev);
   return launch<128, false>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms, dev);
 }

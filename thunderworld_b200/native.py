@@ -81,7 +81,8 @@ class Native:
         return ops.fused_gemm(m, self.n, self.k, packed, self.wc, self.ws_swz, packed.alpha, na=self.na,
                               mask=self.am, wr=self.wr if self.hasw else None, wrs_swz=self.wrs_swz, wi=self.wi,
                               off=self.off, wloc=self.wloc, cross=self.cross, shared=self.shared_bank,
-                              dense=self.dense_w, ws=self.ws, wrs=self.wrs if self.hasw else None, out=out)
+                              dense=self.dense_w, ws=self.ws, wrs=self.wrs if self.hasw else None, out=out,
+                              kernel=getattr(self, 'kernel', 0))
 
     def __call__(self, x):
         if x.ndim != 2 or x.shape[1] != self.k or x.shape[0] <= 0 or ops.cdiv(x.shape[0], 128) != self.am.shape[0]:

@@ -125,7 +125,7 @@ def swizzle(scales):
 
 def fused_gemm(m, n, k, packed, wc, ws_swz, alpha, *, na=0, mask=None, wr=None, wrs_swz=None, wi=None, off=None,
                wloc=None, cross=False, shared=False, dense=False, ws=None, wrs=None, out=None, workspace=None,
-               mask_per_n=False, bias=None):
+               mask_per_n=False, bias=None, kernel=0):
     """One launch of the repaired GEMM; returns bf16 [m,n]."""
     lib = _lib.load()
     dev = wc.device
@@ -141,7 +141,7 @@ def fused_gemm(m, n, k, packed, wc, ws_swz, alpha, *, na=0, mask=None, wr=None, 
                        _ptr(wrs) if hasw else None, _ptr(wi), _ptr(off), _ptr(wloc), _ptr(mask),
                        m, packed.mp, n, k, int(na), int(hasw), int(cross), int(shared), int(dense),
                        int(wr.shape[0]) if hasw else 0, _ptr(a1s) if na else None, _ptr(wrs_swz) if hasw else None,
-                       _ptr(bias), int(mask_per_n))
+                       _ptr(bias), int(mask_per_n), int(kernel))
     with torch.cuda.device(dev):
         _lib.check(lib.tw_fused(m, n, k, packed.codes.data_ptr(), wc.data_ptr(), a0s.data_ptr(), ws_swz.data_ptr(),
                                 out.data_ptr(), alpha.data_ptr(), workspace.data_ptr(), _stream(dev), ctypes.byref(io)))
