@@ -33,7 +33,7 @@ PROJECTIONS = (('qkv', 6144, 2048), ('out', 2048, 2048), ('ffn_up', 8192, 2048),
 NOMINAL_FP4_TFLOPS = 9000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the four fused_kernel<256> launches of one step (M = 7680,
 # 2x plan), from the one-pass full-size ncu capture summarised under profiles/ (bytes per launch, by layer).
-NCU_TRAFFIC_BY_LAYER = {'qkv': 71.1e6, 'out': 18.9e6, 'ffn_up': 103.6e6, 'ffn_down': 81.7e6}
+NCU_TRAFFIC_BY_LAYER = {'qkv': 66.3e6, 'out': 18.8e6, 'ffn_up': 99.5e6, 'ffn_down': 83.7e6}
 NCU_TRAFFIC_BYTES_PER_LAUNCH = sum(NCU_TRAFFIC_BY_LAYER.values()) / len(NCU_TRAFFIC_BY_LAYER)
 
 

@@ -635,7 +635,7 @@ extern "C" int tw_fused(int m, int n, int k, const void* a_codes, const void* w_
   cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
   if (major != 10) return TW_ERR_ARCH;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (io->kernel < 0 || io->kernel > 2) return TW_ERR_ARGUMENT;
+  if (io->kernel < 0 || io->kernel > 3) return TW_ERR_ARGUMENT;
   // 256-wide tiles on CTA pairs (two row blocks per tile) unless the caller asks for the single-CTA kernel
   const bool pair_ok = n % 256 == 0 && !io->mask_per_n && m > 128;
   if (io->kernel == 2 && !pair_ok) return TW_ERR_SHAPE;
@@ -644,7 +644,7 @@ extern "C" int tw_fused(int m, int n, int k, const void* a_codes, const void* w_
   if (pair_ok && io->kernel == 2)
     return tw_fused_pair_launch(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms, dev);
   const bool repair = io->na > 0 || io->hasw;
-  if (n % 256 == 0 && !io->mask_per_n) {
+  if (n % 256 == 0 && !io->mask_per_n && io->kernel != 3) {
     if (repair) return launch<256, true>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms, dev);
     return launch<256, false>(m, n, k, a_codes, w_codes, sfa, sfb, out, alpha, workspace, s, io, sms, dev);
   }

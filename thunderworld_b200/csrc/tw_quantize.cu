@@ -149,22 +149,22 @@ __device__ __forceinline__ uint32_t encode_group2(const float2 (&z)[8], const fl
   return sb;
 }
 
-// grid (K/128, ceil(M/128)); each CTA packs one 128x128 tile of the lattice.
-template <bool PRESCALE, int REPAIR>
-__global__ void __launch_bounds__(PACK_THREADS, 3) pack_kernel(PackParams p) {
-  __shared__ float warp_scores[PACK_THREADS / 32];
-  const int kb = blockIdx.x, mbi = blockIdx.y;
-  const int t = threadIdx.x, cg = t & 7, r0 = t >> 3;
-  const int col = kb * TILE + cg * 16;
-  const float f = load_factor(p);
-  const float rf = __frcp_rn(f);
-  // may the reciprocal sequence replace IEEE division by f? every bf16 numerator mantissa is tried
+// May the reciprocal sequence replace IEEE division by f? Every bf16 numerator mantissa is tried (one per thread
+// of the first four warps); CTA-wide vote.
+__device__ __forceinline__ bool fast_division_ok(float f, float rf) {
   int fast_ok = f > 8.6736174e-19f && f < 1.1529215e18f;        // 2^-60 .. 2^60: no under/overflow inside
-  {
-    const float a = __uint_as_float(0x3f800000u | ((uint32_t)(t & 127) << 16));
-    fast_ok = fast_ok && (div_by(a, f, rf) == __fdiv_rn(a, f));
-  }
-  const bool fast = __syncthreads_and(fast_ok) != 0;
+  const float a = __uint_as_float(0x3f800000u | ((uint32_t)(threadIdx.x & 127) << 16));   // every group of 128 threads tries them all
+  fast_ok = fast_ok && (div_by(a, f, rf) == __fdiv_rn(a, f));
+  return __syncthreads_and(fast_ok) != 0;
+}
+
+// One 128x128 tile of the lattice, packed by the 256 threads of a CTA from `raw` (this thread's 16 consecutive
+// bf16 values of rows pass*32 + r0, pass = 0..3, wherever they were staged).
+template <bool PRESCALE, int REPAIR>
+__device__ __forceinline__ void pack_tile(const PackParams& p, int kb, int mbi, float f, float rf, bool fast,
+                                          const uint4 (&raw)[4][2], float* warp_scores, int group = 0) {
+  const int t = threadIdx.x & (PACK_THREADS - 1), cg = t & 7, r0 = t >> 3;
+  const int col = kb * TILE + cg * 16;
   const int kbn = p.k / TILE;
   const int cols16 = p.k / 16;
   constexpr bool planes2 = REPAIR != 0;
@@ -179,19 +179,6 @@ __global__ void __launch_bounds__(PACK_THREADS, 3) pack_kernel(PackParams p) {
     for (int i = 0; i < 16; ++i) sens[i] = __ldg(p.sensitivity + col + i);
   }
   float2 score2 = make_float2(0.f, 0.f);
-  // all four passes' loads are issued before any arithmetic so that 128 bytes per thread are in flight
-  uint4 raw[4][2];
-#pragma unroll
-  for (int pass = 0; pass < 4; ++pass) {
-    const int row = mbi * TILE + pass * 32 + r0;
-    if (row < p.m) {
-      const uint4* src = reinterpret_cast<const uint4*>(p.x + (size_t)row * p.k + col);
-      raw[pass][0] = __ldg(src);
-      raw[pass][1] = __ldg(src + 1);
-    } else {
-      raw[pass][0] = raw[pass][1] = make_uint4(0u, 0u, 0u, 0u);
-    }
-  }
   auto run = [&](auto fast_tag) {
   constexpr bool FAST = decltype(fast_tag)::value;
 #pragma unroll
@@ -274,18 +261,139 @@ __global__ void __launch_bounds__(PACK_THREADS, 3) pack_kernel(PackParams p) {
     float score = __fadd_rn(score2.x, score2.y);
 #pragma unroll
     for (int o = 16; o; o >>= 1) score = __fadd_rn(score, __shfl_xor_sync(0xffffffffu, score, o));
+    // barriers of the 256 threads that pack this tile (a CTA may hold several such groups)
     if ((t & 31) == 0) warp_scores[t >> 5] = score;
-    __syncthreads();
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "n"(PACK_THREADS) : "memory");
     if (t == 0) {
       float total = 0.f;
       for (int w = 0; w < PACK_THREADS / 32; ++w) total = __fadd_rn(total, warp_scores[w]);
       p.scores[mbi * kbn + kb] = total;
     }
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "n"(PACK_THREADS) : "memory");   // warp_scores is reused by the next tile
   }
-  if (blockIdx.x == 0 && blockIdx.y == 0 && t == 0) {
-    if (!p.factor_given) *p.factor = f;
-    if (p.alpha && p.wg) *p.alpha = __fmul_rn(f, *p.wg);
+}
+
+// This thread's share of tile (mbi, kb): four rows, 32 bytes each; rows beyond m read as zeros.
+__device__ __forceinline__ void load_tile_rows(const PackParams& p, int kb, int mbi, uint4 (&raw)[4][2]) {
+  const int t = threadIdx.x & (PACK_THREADS - 1), cg = t & 7, r0 = t >> 3;
+  const int col = kb * TILE + cg * 16;
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const int row = mbi * TILE + pass * 32 + r0;
+    if (row < p.m) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.x + (size_t)row * p.k + col);
+      raw[pass][0] = __ldg(src);
+      raw[pass][1] = __ldg(src + 1);
+    } else {
+      raw[pass][0] = raw[pass][1] = make_uint4(0u, 0u, 0u, 0u);
+    }
   }
+}
+
+__device__ __forceinline__ void publish_factor(const PackParams& p, float f) {
+  if (!p.factor_given) *p.factor = f;
+  if (p.alpha && p.wg) *p.alpha = __fmul_rn(f, *p.wg);
+}
+
+// Two-launch form (the factor comes from amax_kernel or from the producer of x):
+// grid (K/128, ceil(M/128)); each CTA packs one 128x128 tile of the lattice.
+template <bool PRESCALE, int REPAIR>
+__global__ void __launch_bounds__(PACK_THREADS, 3) pack_kernel(PackParams p) {
+  __shared__ float warp_scores[PACK_THREADS / 32];
+  const int kb = blockIdx.x, mbi = blockIdx.y;
+  const float f = load_factor(p);
+  const float rf = __frcp_rn(f);
+  const bool fast = fast_division_ok(f, rf);
+  // all four passes' loads are issued before any arithmetic so that 128 bytes per thread are in flight
+  uint4 raw[4][2];
+  load_tile_rows(p, kb, mbi, raw);
+  pack_tile<PRESCALE, REPAIR>(p, kb, mbi, f, rf, fast, raw, warp_scores);
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) publish_factor(p, f);
+}
+
+// Single-pass form: x is read from global memory once. A cooperative grid of resident CTAs (one per SM) parks
+// its tiles in shared memory while it reduces max|bf16(x d)|, meets at a grid barrier, and packs from shared
+// memory under the tensor factor. Used when the tensor fits (tiles <= RESIDENT_TILES per CTA) and the caller
+// gives no factor. The barrier wait is bounded: on a timeout (it cannot happen under a cooperative launch, which
+// guarantees that every CTA is resident) the status word is set and the CTA returns.
+constexpr int RESIDENT_TILES = 7;                        // 7 x 32 KB of the 227 KB a CTA may hold
+constexpr int RESIDENT_GROUPS = 2;                       // groups of PACK_THREADS threads, each packs one tile at a time
+template <bool PRESCALE, int REPAIR>
+__global__ void __launch_bounds__(RESIDENT_GROUPS * PACK_THREADS, 1) pack_resident_kernel(PackParams p, int tiles, unsigned* header) {
+  extern __shared__ uint4 slab[];                        // [tile slot][pass][256 threads][2]
+  __shared__ float warp_scores[RESIDENT_GROUPS][PACK_THREADS / 32];
+  __shared__ float warp_peak[RESIDENT_GROUPS * PACK_THREADS / 32];
+  __shared__ int give_up;
+  const int t = threadIdx.x & (PACK_THREADS - 1), group = threadIdx.x / PACK_THREADS;
+  const int kbn = p.k / TILE;
+  float peak = 0.f;
+  __nv_bfloat162 pk = __floats2bfloat162_rn(0.f, 0.f);
+  // this CTA's tiles are blockIdx.x, + gridDim.x, ...; its groups take them alternately; slot = position in the CTA
+  int slot = group;
+  for (int tile = blockIdx.x + group * gridDim.x; tile < tiles; tile += RESIDENT_GROUPS * gridDim.x, slot += RESIDENT_GROUPS) {
+    const int mbi = tile / kbn, kb = tile % kbn;
+    uint4 raw[4][2];
+    load_tile_rows(p, kb, mbi, raw);
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        slab[((slot * 4 + pass) * 2 + j) * PACK_THREADS + t] = raw[pass][j];
+        const uint32_t w[4] = {raw[pass][j].x, raw[pass][j].y, raw[pass][j].z, raw[pass][j].w};
+        if (PRESCALE) {
+          const float* d = p.prescale + kb * TILE + (t & 7) * 16 + j * 8;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float lo = tw::bf16_bits_to_float(w[q] & 0xffffu), hi = tw::bf16_bits_to_float(w[q] >> 16);
+            lo = __bfloat162float(__float2bfloat16_rn(__fmul_rn(lo, __ldg(d + 2 * q))));
+            hi = __bfloat162float(__float2bfloat16_rn(__fmul_rn(hi, __ldg(d + 2 * q + 1))));
+            peak = fmaxf(peak, fmaxf(fabsf(lo), fabsf(hi)));
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) pk = __hmax2(pk, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[q])));
+        }
+      }
+    }
+  }
+  if (!PRESCALE) peak = fmaxf(__low2float(pk), __high2float(pk));
+#pragma unroll
+  for (int o = 16; o; o >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, o));
+  if ((threadIdx.x & 31) == 0) warp_peak[threadIdx.x >> 5] = peak;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int w = 1; w < RESIDENT_GROUPS * PACK_THREADS / 32; ++w) peak = fmaxf(peak, warp_peak[w]);
+    if (peak > 0.f) atomicMax(header, __float_as_uint(peak));
+    __threadfence();
+    atomicAdd(header + 1, 1u);
+    // grid barrier, bounded
+    int bad = 0;
+    const long long start = clock64();
+    while (atomicAdd(header + 1, 0u) < gridDim.x) {
+      __nanosleep(40);
+      if (clock64() - start > 1000000000LL) { bad = 1; atomicExch(header + 2, (unsigned)TW_ERR_TIMEOUT); break; }
+    }
+    __threadfence();
+    give_up = bad;
+  }
+  __syncthreads();
+  if (give_up) return;
+  const float f = load_factor(p);
+  const float rf = __frcp_rn(f);
+  const bool fast = fast_division_ok(f, rf);
+  slot = group;
+  for (int tile = blockIdx.x + group * gridDim.x; tile < tiles; tile += RESIDENT_GROUPS * gridDim.x, slot += RESIDENT_GROUPS) {
+    const int mbi = tile / kbn, kb = tile % kbn;
+    uint4 raw[4][2];
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+      raw[pass][0] = slab[((slot * 4 + pass) * 2 + 0) * PACK_THREADS + t];
+      raw[pass][1] = slab[((slot * 4 + pass) * 2 + 1) * PACK_THREADS + t];
+    }
+    pack_tile<PRESCALE, REPAIR>(p, kb, mbi, f, rf, fast, raw, warp_scores[group], group);
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) publish_factor(p, f);
 }
 
 // Per M128 row block: rank K128 blocks by score (descending, lower index wins ties), keep rank < na,
@@ -348,15 +456,6 @@ extern "C" int tw_quantize(const TwQuantizeArgs* a, void* stream_) {
   unsigned* amax = static_cast<unsigned*>(a->workspace);
   float* scores = reinterpret_cast<float*>(static_cast<char*>(a->workspace) + 256);
   const int mb = (a->m + 127) / 128, kb = a->k / 128;
-  if (!a->factor_given) {
-    if (cudaMemsetAsync(amax, 0, sizeof(unsigned), stream) != cudaSuccess) return TW_ERR_LAUNCH;
-    long long vecs = (long long)a->m * a->k / 8;
-    int blocks = (int)((vecs + 1023) / 1024 < 148 * 8 ? (vecs + 1023) / 1024 : 148 * 8);
-    if (a->prescale)
-      amax_kernel<true><<<blocks, 256, 0, stream>>>(static_cast<const uint4*>(a->x), a->prescale, vecs, a->k, amax);
-    else
-      amax_kernel<false><<<blocks, 256, 0, stream>>>(static_cast<const uint4*>(a->x), nullptr, vecs, a->k, amax);
-  }
   PackParams p{};
   p.x = static_cast<const __nv_bfloat16*>(a->x);
   p.prescale = a->prescale; p.sensitivity = a->sensitivity;
@@ -366,9 +465,46 @@ extern "C" int tw_quantize(const TwQuantizeArgs* a, void* stream_) {
   p.m = a->m; p.k = a->k; p.mp = a->mp; p.mb = mb;
   p.repair = a->repair; p.factor_given = a->factor_given;
   p.base = a->base; p.res = a->res; p.gain = a->gain;
+  int dev = 0, sms = 0, coop = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TW_ERR_LAUNCH;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+  const long long tiles = (long long)mb * kb;
+  // single pass when the tensor can stay in shared memory between the reduction and the packing
+  const bool resident = !a->factor_given && coop && sms > 0 && tiles <= (long long)RESIDENT_TILES * sms;
+  if (!a->factor_given && cudaMemsetAsync(amax, 0, 16, stream) != cudaSuccess) return TW_ERR_LAUNCH;
+  if (!a->factor_given && !resident) {
+    long long vecs = (long long)a->m * a->k / 8;
+    int blocks = (int)((vecs + 1023) / 1024 < 148 * 8 ? (vecs + 1023) / 1024 : 148 * 8);
+    if (a->prescale)
+      amax_kernel<true><<<blocks, 256, 0, stream>>>(static_cast<const uint4*>(a->x), a->prescale, vecs, a->k, amax);
+    else
+      amax_kernel<false><<<blocks, 256, 0, stream>>>(static_cast<const uint4*>(a->x), nullptr, vecs, a->k, amax);
+  }
   dim3 grid(kb, mb);
+  int status = TW_OK;
   auto launch = [&](auto pre, auto mode) {
-    pack_kernel<decltype(pre)::value, decltype(mode)::value><<<grid, PACK_THREADS, 0, stream>>>(p);
+    constexpr bool PRE = decltype(pre)::value;
+    constexpr int MODE = decltype(mode)::value;
+    if (!resident) {
+      pack_kernel<PRE, MODE><<<grid, PACK_THREADS, 0, stream>>>(p);
+      return;
+    }
+    const int ctas = tiles < sms ? (int)tiles : sms;
+    const int per_cta = (int)((tiles + ctas - 1) / ctas);
+    const int smem = per_cta * TILE * TILE * 2;
+    static std::atomic<int> configured[64];                  // largest opt-in made so far on this device
+    if (configured[dev].load(std::memory_order_acquire) < smem) {
+      if (cudaFuncSetAttribute(pack_resident_kernel<PRE, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               RESIDENT_TILES * TILE * TILE * 2) != cudaSuccess) { status = TW_ERR_LAUNCH; return; }
+      configured[dev].store(RESIDENT_TILES * TILE * TILE * 2, std::memory_order_release);
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(ctas); cfg.blockDim = dim3(RESIDENT_GROUPS * PACK_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative; attr[0].val.cooperative = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, pack_resident_kernel<PRE, MODE>, p, (int)tiles, amax) != cudaSuccess) status = TW_ERR_LAUNCH;
   };
   auto by_mode = [&](auto pre) {
     switch (a->repair) {
@@ -379,6 +515,7 @@ extern "C" int tw_quantize(const TwQuantizeArgs* a, void* stream_) {
     }
   };
   if (a->prescale) by_mode(std::true_type{}); else by_mode(std::false_type{});
+  if (status != TW_OK) return status;
   if (a->repair == 3) choose_kernel<<<mb, 128, kb * sizeof(float), stream>>>(scores, a->mask, kb, a->na, a->energy);
   return cudaGetLastError() == cudaSuccess ? TW_OK : TW_ERR_LAUNCH;
 }

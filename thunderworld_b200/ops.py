@@ -148,20 +148,20 @@ def fused_gemm(m, n, k, packed, wc, ws_swz, alpha, *, na=0, mask=None, wr=None, 
     return out
 
 
-STATUS_KEYS = ('g', 'a')       # workspaces whose first word is a device status word: fused GEMM, attention
+STATUS_KEYS = {'g': 0, 'a': 0, 'q': 8}   # workspace -> byte offset of its device status word: fused GEMM, attention, quantizer
 
 
 def device_status(device=None):
     """Worst status word any kernel of this device wrote on a bounded-wait timeout (0 = none); synchronises.
-    Covers the fused GEMM and the attention kernel: each writes into the first word of its own workspace."""
+    Covers the fused GEMM, the attention kernel and the single-pass quantizer's grid barrier: each writes into its own workspace."""
     dev = torch.device('cuda', torch.cuda.current_device()) if device is None else torch.device(device)
     if dev.index is None:
         dev = torch.device('cuda', torch.cuda.current_device())
     worst = 0
-    for key in STATUS_KEYS:
+    for key, offset in STATUS_KEYS.items():
         ws = _workspaces.get((dev, key))
         if ws is not None:
-            worst = max(worst, int(ws[:4].view(torch.int32).item()))
+            worst = max(worst, int(ws[offset:offset + 4].view(torch.int32).item()))
     return worst
 
 
@@ -170,10 +170,10 @@ def reset_device_status(device=None):
     dev = torch.device('cuda', torch.cuda.current_device()) if device is None else torch.device(device)
     if dev.index is None:
         dev = torch.device('cuda', torch.cuda.current_device())
-    for key in STATUS_KEYS:
+    for key, offset in STATUS_KEYS.items():
         ws = _workspaces.get((dev, key))
         if ws is not None:
-            ws[:4].zero_()
+            ws[offset:offset + 4].zero_()
 
 
 # ---- pointwise producers with fused tensor factor -----------------------------------------------
