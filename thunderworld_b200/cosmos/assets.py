@@ -1,7 +1,10 @@
 """W1-support storage: keep only the residual-weight tiles a plan can ever select, and restore the dense
 planes from that compact form. Same dictionary keys and schemas (1 = top-fraction by score, 2 = explicit
 tile list) as packages/fp4-repair/src/thunderworld_fp4/cosmos/assets.py:26-66, so assets interchange."""
+import hashlib
+import json
 import math
+from pathlib import Path
 import torch
 from .budget import support
 
@@ -61,3 +64,38 @@ def expand(asset, required):
         residual = tiles.reshape(nb, kb, 128, width).permute(0, 2, 1, 3).reshape(base.shape)
         out[name] = torch.stack((base.view(torch.uint8), residual)).view(base.dtype)
     return out
+
+
+def export_assets(folder, assets, *, model_identity, precision='fp4', targets=(), support=None):
+    """Write prepared per-module assets as `NNNN.pt` plus a `manifest.json` holding each file's sha256, the same
+    directory layout as the reference's `prepare --export` (cosmos/runner.py:109-119). `support`: optional
+    {module name: fraction or tile ids} -> the asset is stored in compact form."""
+    folder = Path(folder)
+    folder.mkdir(parents=True, exist_ok=False)
+    manifest = dict(complete=False, model_identity=model_identity, precision=precision, targets=list(targets), modules={})
+    for i, (name, asset) in enumerate(assets.items()):
+        if precision == 'fp4' and support is not None:
+            asset = compact(asset, support[name])
+        path = folder / f'{i:04d}.pt'
+        torch.save(asset, path)
+        manifest['modules'][name] = dict(file=path.name, sha256=hashlib.sha256(path.read_bytes()).hexdigest())
+    manifest['complete'] = True
+    (folder / 'manifest.json').write_text(json.dumps(manifest, indent=2) + '\n')
+    return manifest
+
+
+def load_assets(folder, *, model_identity, precision='fp4', required=None):
+    """Inverse of export_assets (reference: cosmos/runner.py:82-92): refuses an incomplete manifest, another
+    model or precision and any file whose hash changed; expands compact assets to the `required` support."""
+    folder = Path(folder)
+    manifest = json.loads((folder / 'manifest.json').read_text())
+    if not manifest['complete'] or manifest['model_identity'] != model_identity or manifest['precision'] != precision:
+        raise ValueError('Prepared asset/model/precision mismatch')
+    assets = {}
+    for name, entry in manifest['modules'].items():
+        path = folder / entry['file']
+        if hashlib.sha256(path.read_bytes()).hexdigest() != entry['sha256']:
+            raise ValueError('Corrupt prepared asset')
+        asset = torch.load(path, weights_only=True, map_location='cpu')
+        assets[name] = expand(asset, required[name]) if precision == 'fp4' and required is not None else asset
+    return assets
