@@ -30,6 +30,10 @@ extern "C" {
 const char* tw_status(int status);
 /* Library ABI version (bumped when a struct below changes). */
 int tw_abi_version(void);
+/* Self-test of the bounded device-side waits (no counterpart in the reference): launches one small CTA whose
+ * warps wait on a barrier that nothing signals; after `limit_cycles` SM cycles they give up and the first word of
+ * `workspace` becomes the "bounded device-side wait ran out" status. The GPU is neither hung nor faulted. */
+int tw_selftest_bounded_wait(void* workspace, long long limit_cycles, void* stream);
 
 /* ---- activation quantizer ------------------------------------------------------------------
  * One call replaces the reference's launch chain scaled_amax -> finish_amax -> pack_activation
@@ -70,6 +74,11 @@ int tw_quantize(const TwQuantizeArgs* args, void* stream);
  * calls on a device share the array: calls that overlap on the GPU race. Allocates nothing. */
 int tw_quantize_static(const TwQuantizeArgs* args, void* stream);
 int tw_quantize_static_max_tiles(void);
+
+/* Sampled-energy rank of every K128 block within its M128 row block: rank int32 [ceil(m/128), k/128], 0 = largest
+ * (eight rows x eight columns of bf16(x * prescale) per 128x128 block; the lower index wins ties). prescale may be
+ * NULL. Replaces activation_rank of thunderworld_fp4/_linear_kernels.py:23-34 (one launch, no host sync). */
+int tw_activation_rank(const void* x_bf16, const float* prescale, int m, int k, int32_t* rank, void* stream);
 
 /* Row-major E4M3 scale bytes [rows, cols] -> atom layout [ceil(rows/128)*128, cols], padding zeroed.
  * Replaces thunderworld_fp4/cutlass/layout.py:7-25 (swizzle). cols % 4 == 0. */

@@ -59,6 +59,53 @@ def test_fp4linear_explicit_mask_per_output_block():
         layer(torch.from_numpy(x).cuda().bfloat16(), repair_mask=torch.zeros(3, 3, 3, device='cuda', dtype=torch.bool))
 
 
+def torch_block_rank(x, prescale, m, k):
+    """The sampled-energy ranking in plain torch (the checker of the CUDA activation_rank kernel): eight rows and
+    eight columns (every 16th) of bf16(x*d) per 128x128 block, stable descending argsort."""
+    mb, kb = (m + 127) // 128, k // 128
+    rows = (torch.arange(mb, device=x.device)[:, None] * 128 + torch.arange(8, device=x.device)[None, :] * 16)
+    rows = rows.clamp_max(m - 1).reshape(-1)
+    sample = (x[rows][:, ::16].float() * prescale[::16]).bfloat16().float()
+    energy = sample.square().reshape(mb, 8, kb, 8).sum((1, 3))
+    order = torch.argsort(energy, dim=1, descending=True, stable=True)
+    rank = torch.empty_like(order)
+    rank.scatter_(1, order, torch.arange(kb, device=x.device).expand(mb, kb))
+    return rank.int()
+
+
+@pytest.mark.parametrize('m,k', [(256, 1024), (300, 2048), (129, 24576)])
+def test_activation_rank_kernel_matches_torch_ranking(m, k):
+    from thunderworld_b200 import ops
+    x = torch.from_numpy(o.synthetic_activation(m, k, 6)).cuda().bfloat16()
+    d = (torch.rand(k, device='cuda') * 1.5 + .5)
+    for prescale in (None, d):
+        got = ops.activation_rank(x, prescale)
+        want = torch_block_rank(x, torch.ones(k, device='cuda') if prescale is None else prescale, m, k)
+        assert got.shape == want.shape and got.dtype == torch.int32
+        assert sorted(got[0].tolist()) == list(range(k // 128))
+        # float32 summation order may swap blocks of (nearly) equal energy
+        assert (got != want).float().mean() < 0.02
+
+
+def test_fp4linear_explicit_mask_with_256_wide_outputs():
+    """An explicit [M128, N128, K128] mask with N a multiple of 256: one A support per output block, which only
+    the 128-wide tiles can honour."""
+    from thunderworld_b200.linear import FP4Linear
+    from thunderworld_b200.config import LinearRepairConfig
+    m, n, k = 384, 512, 512
+    x = o.synthetic_activation(m, k, 9)
+    w = o.synthetic_weight(n, k, 9)
+    layer = FP4Linear.from_float(torch.from_numpy(w).cuda().bfloat16(), config=LinearRepairConfig(coverage=0.5))
+    mask = np.random.default_rng(9).random((3, 4, 4)) < 0.4
+    y = layer(torch.from_numpy(x).cuda().bfloat16(), repair_mask=torch.from_numpy(mask).cuda())
+    wc, wsb, wf = o.quantize_weight(w)
+    ac, asb, af = o.quantize_linear_input(x, rows_padded=384)
+    ac, asb = o.zero_unselected_residual(ac, asb, mask.any(1))
+    want = np.concatenate([o.repair_linear(ac, asb, af, wc[:, nb * 128:(nb + 1) * 128], wsb[:, nb * 128:(nb + 1) * 128], wf, m,
+                                           a_mask=mask[:, nb]) for nb in range(4)], axis=1)
+    assert rel_l2(y.float().cpu().numpy(), want) <= TOL
+
+
 def test_fp4linear_partial_coverage_uses_sampled_ranking():
     from thunderworld_b200.linear import FP4Linear, sampled_block_rank
     from thunderworld_b200.config import LinearRepairConfig
@@ -124,9 +171,9 @@ def test_repair_linear_follows_the_plan_per_phase():
             assert mask.sum(1).tolist() == [na] * 3
             want_mask = o.choose_blocks(scores, na)
             assert (mask != want_mask).sum() <= 2          # float32 summation order near ties
+        # the bias joins the fp32 accumulator before the single bf16 rounding (TwRepairIO.bias)
         want = o.repair_linear(ac, asb, af, wc, wsb, wf, m, a_mask=mask, a_full=na == kb, w_tiles=row['w_blocks'],
-                               cross=row['cross'], round_bf16=True)
-        want = o.bf16_round(want + bias[None, :])
+                               cross=row['cross'], bias=bias, round_bf16=True)
         assert rel_l2(y.float().cpu().numpy(), want) <= TOL, ph
     # all operators share W0 and the union bank
     ops_ = list(layer.ops.values())

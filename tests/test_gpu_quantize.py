@@ -101,6 +101,40 @@ def test_online_selector_mask_matches_oracle_ranking():
     assert np.array_equal(as_np(p.codes), codes)
 
 
+@pytest.mark.parametrize('energy', [0.5, 0.75])
+def test_online_selector_energy_prefix_stop(energy):
+    """The energy-prefix stop: a K128 block is kept only while the blocks ranked before it hold less than `energy`
+    of the row block's total score (thunderworld_fp4/_sparse_pack.py:54-60), so fewer than `na` blocks may be kept."""
+    m, k, na = 300, 1024, 4
+    x = o.synthetic_activation(m, k, 12)
+    x[:, :128] *= 6                                   # one dominant block: the prefix stops early
+    x = o.bf16_round(x)
+    sens = (np.random.default_rng(4).random(k) + 0.5).astype(np.float32)
+    scores, _ = o.residual_scores(x, None, sens)
+    want = o.choose_blocks(scores, na, energy)
+    p = gpu_quantize(x, repair=3, na=na, sensitivity=torch.from_numpy(sens).cuda(), energy=energy)
+    got = p.mask.cpu().numpy()
+    assert (got.sum(1) <= na).all() and (want.sum(1) < na).any()
+    assert np.array_equal(got, want)
+
+
+def test_bounded_wait_runs_out_and_is_reported():
+    """A wait that nothing will ever satisfy ends after its cycle limit with a status code, and the GPU goes on
+    working: no trap, no hang, nothing left in flight."""
+    from thunderworld_b200 import ops
+    ops.reset_device_status()
+    assert ops.device_status() == 0
+    status = ops.selftest_bounded_wait(limit_cycles=500_000)
+    assert status == 8                                # TW_ERR_TIMEOUT
+    from thunderworld_b200 import _lib
+    assert b'wait ran out' in _lib.load().tw_status(status)
+    ops.reset_device_status()
+    assert ops.device_status() == 0
+    x = o.synthetic_activation(64, 256, 1)
+    codes, _, _ = o.quantize_linear_input(x, rows_padded=64)
+    assert np.array_equal(as_np(gpu_quantize(x, repair=1).codes), codes)     # the context is intact
+
+
 def test_rejects_bad_arguments():
     from thunderworld_b200 import ops
     with pytest.raises(ValueError):

@@ -82,6 +82,8 @@ def load():
     lib.tw_quantize_static.argtypes = [ctypes.POINTER(QuantizeArgs), _vp]; lib.tw_quantize_static.restype = _i
     lib.tw_quantize_static_max_tiles.argtypes = []; lib.tw_quantize_static_max_tiles.restype = _i
     lib.tw_swizzle_scales.argtypes = [_vp, _i, _i, _vp, _vp]; lib.tw_swizzle_scales.restype = _i
+    lib.tw_activation_rank.argtypes = [_vp, _vp, _i, _i, _vp, _vp]; lib.tw_activation_rank.restype = _i
+    lib.tw_selftest_bounded_wait.argtypes = [_vp, _ll, _vp]; lib.tw_selftest_bounded_wait.restype = _i
     lib.tw_workspace.argtypes = [_i] * 3; lib.tw_workspace.restype = ctypes.c_size_t
     lib.tw_fused.argtypes = [_i] * 3 + [_vp] * 8 + [ctypes.POINTER(RepairIO)]; lib.tw_fused.restype = _i
     lib.tw_fused_tile_n.argtypes = [_i]; lib.tw_fused_tile_n.restype = _i
@@ -108,6 +110,6 @@ def check(status):
 
 
 EXPORTS = ('tw_status', 'tw_abi_version', 'tw_quantize_workspace', 'tw_quantize', 'tw_quantize_static',
-           'tw_quantize_static_max_tiles', 'tw_swizzle_scales',
+           'tw_quantize_static_max_tiles', 'tw_swizzle_scales', 'tw_activation_rank', 'tw_selftest_bounded_wait',
            'tw_workspace', 'tw_fused', 'tw_fused_tile_n', 'tw_pack_rows', 'tw_select_tiles', 'tw_attention',
            'tw_attention_workspace', 'tw_activate', 'tw_rms_norm', 'tw_rms_norm_heads', 'tw_gate_residual')

@@ -133,8 +133,8 @@ class RepairLinear(torch.nn.Module):
                 mode = 0 if op.na == 0 else (1 if op.na == kb else 2)
                 use_factor = factor if (base, res) == (1., 1.) else None
                 packed = ops.quantize(x, d, repair=mode, mask=op.am if mode == 2 else None, factor=use_factor, **common)
-        y = op.run_packed(x, packed)
-        return y if self.bias is None else y + self.bias
+        # the bias is added in fp32 before the single bf16 rounding of the epilogue (TwRepairIO.bias)
+        return op.run_packed(x, packed, bias=self.bias)
 
     def forward(self, x, *, factor=None, packed=None):
         shape = x.shape

@@ -422,6 +422,36 @@ __global__ void __launch_bounds__(128) choose_kernel(const float* __restrict__ s
   }
 }
 
+// Sampled-energy rank of every K128 block within its M128 row block (reference: activation_rank,
+// thunderworld_fp4/_linear_kernels.py:23-34): eight rows (every 16th, clamped to the last row) and eight columns
+// (every 16th) of bf16(x * d) per 128x128 block; rank 0 = largest energy, the lower index wins ties.
+__global__ void __launch_bounds__(128) rank_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ d,
+                                                   int m, int k, int* __restrict__ rank) {
+  extern __shared__ float energy[];
+  const int mb = blockIdx.x, kbn = k / TILE;
+  for (int kb = threadIdx.x; kb < kbn; kb += blockDim.x) {
+    float e = 0.f;
+    for (int i = 0; i < 8; ++i) {
+      const int row = min(mb * TILE + i * 16, m - 1);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int col = kb * TILE + j * 16;
+        float v = __bfloat162float(x[(size_t)row * k + col]);
+        if (d) v = __bfloat162float(__float2bfloat16_rn(__fmul_rn(v, __ldg(d + col))));
+        e = __fmaf_rn(v, v, e);
+      }
+    }
+    energy[kb] = e;
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < kbn; j += blockDim.x) {
+    const float mine = energy[j];
+    int r = 0;
+    for (int o = 0; o < kbn; ++o) r += (energy[o] > mine) || (energy[o] == mine && o < j);
+    rank[mb * kbn + j] = r;
+  }
+}
+
 __global__ void __launch_bounds__(256) swizzle_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
                                                       int rows, int cols, int rows_padded) {
   // one thread per 4 consecutive scale columns of one row
@@ -517,6 +547,14 @@ extern "C" int tw_quantize(const TwQuantizeArgs* a, void* stream_) {
   if (a->prescale) by_mode(std::true_type{}); else by_mode(std::false_type{});
   if (status != TW_OK) return status;
   if (a->repair == 3) choose_kernel<<<mb, 128, kb * sizeof(float), stream>>>(scores, a->mask, kb, a->na, a->energy);
+  return cudaGetLastError() == cudaSuccess ? TW_OK : TW_ERR_LAUNCH;
+}
+
+extern "C" int tw_activation_rank(const void* x, const float* prescale, int m, int k, int32_t* rank, void* stream_) {
+  if (!x || !rank || m <= 0 || k <= 0) return TW_ERR_ARGUMENT;
+  if (k % 128) return TW_ERR_SHAPE;
+  const int mb = (m + 127) / 128, kb = k / 128;
+  rank_kernel<<<mb, 128, kb * sizeof(float), static_cast<cudaStream_t>(stream_)>>>(static_cast<const __nv_bfloat16*>(x), prescale, m, k, rank);
   return cudaGetLastError() == cudaSuccess ? TW_OK : TW_ERR_LAUNCH;
 }
 

@@ -123,6 +123,29 @@ def swizzle(scales):
     return out
 
 
+def activation_rank(x, prescale=None):
+    """int32 [ceil(m/128), k/128]: rank of every K128 block within its M128 row block by sampled energy
+    (reference: activation_rank, thunderworld_fp4/_linear_kernels.py:23-34). One launch, no host sync."""
+    if x.ndim != 2 or x.dtype != torch.bfloat16 or not x.is_contiguous() or x.shape[1] % 128 or x.shape[0] == 0:
+        raise ValueError('expected contiguous BF16 [M,K] with K a multiple of 128')
+    require_sm100(x.device)
+    m, k = x.shape
+    rank = torch.empty((cdiv(m, 128), k // 128), device=x.device, dtype=torch.int32)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().tw_activation_rank(_ptr(x), _ptr(prescale), m, k, _ptr(rank), _stream(x.device)))
+    return rank
+
+
+def selftest_bounded_wait(device=None, limit_cycles=2_000_000):
+    """Make a bounded device-side wait run out on purpose (a barrier nothing signals) and return the status word
+    that `device_status` then reports; the word is left set so that the caller can see and reset it."""
+    dev = torch.device('cuda', torch.cuda.current_device()) if device is None else torch.device(device)
+    ws = _workspace(dev, 256, 'g')
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().tw_selftest_bounded_wait(_ptr(ws), int(limit_cycles), _stream(dev)))
+    return device_status(dev)
+
+
 def fused_gemm(m, n, k, packed, wc, ws_swz, alpha, *, na=0, mask=None, wr=None, wrs_swz=None, wi=None, off=None,
                wloc=None, cross=False, shared=False, dense=False, ws=None, wrs=None, out=None, workspace=None,
                mask_per_n=False, bias=None, kernel=0):
