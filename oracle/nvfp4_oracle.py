@@ -499,6 +499,17 @@ def rms_norm(x, weight=None, eps=1e-6, shift=None, scale=None):
     return y, finish_factor(y)
 
 
+def rope(x, cos, sin):
+    """fused_rope (cosmos/pipeline_tuning.py:42-63): x [..., tokens, heads, D] bf16 values, cos / sin [tokens, D];
+    y = bf16(bf16(x cos) + bf16(rot sin)) with rot = (-x[D/2:], x[:D/2]); both products are rounded to bf16 first."""
+    x = np.asarray(x, dtype=F32)
+    d = x.shape[-1]
+    rot = np.concatenate([-x[..., d // 2:], x[..., :d // 2]], -1)
+    c = np.asarray(cos, dtype=F32)[:, None, :]
+    s_ = np.asarray(sin, dtype=F32)[:, None, :]
+    return bf16_round(bf16_round(x * c) + bf16_round(rot * s_))
+
+
 def gate_residual(x, gate, y):
     """bf16(x + gate[:, None] * y): the product of two bf16 values and its sum with a third are exact in
     float64 for magnitudes of interest, so float32 then bf16 rounding reproduces a float32 fma."""

@@ -78,7 +78,7 @@ def test_budget_check_fails_closed():
 def test_repaired_step_tracks_the_unquantized_model():
     """Sanity of the whole block arithmetic: full repair stays close to a bf16 torch forward of the
     same weights (loose bound; operator-level parity is tested against the oracle elsewhere)."""
-    from thunderworld_b200.cosmos.dit import DiTConfig, DiTModel, rms_norm
+    from thunderworld_b200.cosmos.dit import DiTConfig, DiTModel, rms_norm, rope_tables, apply_rope
     from thunderworld_b200.cosmos.engine import StepEngine
     from thunderworld_b200.cosmos.settings import LinearSpec, RunConfig
     from thunderworld_b200.config import RepairConfig, RepairPolicy
@@ -99,7 +99,8 @@ def test_repaired_step_tracks_the_unquantized_model():
     s1, c1, g1, s2, c2, g2 = m.unbind(1)
     hcur = rms_norm(xf) * (1 + c1[:, None]) + s1[:, None]
     q, k, v = (hcur @ w['qkv'].T).reshape(2, 200, 3, 2, 128).unbind(2)
-    q, k = rms_norm(q), rms_norm(k)
+    cos, sin = rope_tables(200, 'cuda')
+    q, k = apply_rope(rms_norm(q), cos, sin), apply_rope(rms_norm(k), cos, sin)
     att = torch.softmax(torch.einsum('bshd,bthd->bhst', q, k) / 128 ** .5, -1)
     a = torch.einsum('bhst,bthd->bshd', att, v).reshape(2, 200, 256)
     xf = xf + g1[:, None] * (a @ w['out'].T)

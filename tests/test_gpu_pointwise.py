@@ -126,3 +126,25 @@ def test_argument_errors():
     b = torch.zeros(4, 129, device='cuda', dtype=torch.bfloat16)
     with pytest.raises(RuntimeError):                   # n % 8 != 0 -> status from the C ABI
         ops.activate_with_factor(b)
+
+
+@pytest.mark.parametrize('table_dtype', [torch.float32, torch.bfloat16])
+def test_rope_heads_bit_exact_and_fused_with_head_norm(table_dtype):
+    """Exact-rounding RoPE: bit for bit against the oracle; running it after the head norm in the same kernel gives
+    the bytes of the two kernels run one after the other; strided q / k views of a fused QKV output are accepted."""
+    from thunderworld_b200 import ops
+    from thunderworld_b200.cosmos.dit import rope_tables
+    g = torch.Generator().manual_seed(3)
+    b, s, h = 2, 75, 3
+    qkv = torch.randn(b, s, 3, h, 128, generator=g).bfloat16().cuda()
+    cos, sin = (t.to(table_dtype) for t in rope_tables(s, 'cuda'))
+    q = qkv[:, :, 0]                                              # strided view [b, s, h, 128]
+    got = ops.rope_heads(q, cos, sin)
+    want = O.rope(q.float().cpu().numpy(), np.tile(cos.float().cpu().numpy(), (b, 1)).reshape(b, s, 128)[0],
+                  sin.float().cpu().numpy())
+    assert np.array_equal(got.float().cpu().numpy(), want)
+    fused = ops.rope_heads(q, cos, sin, norm=True)
+    two = ops.rope_heads(ops.rms_norm_heads(q), cos, sin)
+    assert torch.equal(fused, two)
+    with pytest.raises(ValueError):
+        ops.rope_heads(q, cos[:, :64].contiguous(), sin[:, :64].contiguous())

@@ -39,3 +39,17 @@ def test_gate_residual_matches_float32_fma():
     g = torch.randn(2, 64).bfloat16()
     want = torch.addcmul(x.double(), g.double()[:, None], y.double()).float().bfloat16().float().numpy()
     assert np.array_equal(O.gate_residual(x.float().numpy(), g.float().numpy(), y.float().numpy()), want)
+
+
+def test_rope_matches_bf16_torch_arithmetic():
+    """The reference's RoPE kernel reproduces PyTorch's bf16 evaluation, which materialises both bf16 products before
+    the bf16 addition (cosmos/pipeline_tuning.py:53-55); the oracle must equal that evaluation bit for bit."""
+    import torch
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(2, 17, 3, 128, generator=g).bfloat16()
+    ang = torch.rand(17, 128, generator=g) * 6
+    cos, sin = ang.cos().bfloat16(), ang.sin().bfloat16()
+    rot = torch.cat([-x[..., 64:], x[..., :64]], -1)
+    want = x * cos[:, None, :] + rot * sin[:, None, :]                      # bf16 mul, bf16 mul, bf16 add
+    got = O.rope(x.float().numpy(), cos.float().numpy(), sin.float().numpy())
+    assert np.array_equal(got, want.float().numpy())

@@ -94,6 +94,7 @@ def load():
     lib.tw_activate.argtypes = [_vp] * 5 + [_ll, _i, _vp]; lib.tw_activate.restype = _i
     lib.tw_rms_norm.argtypes = [_vp] * 7 + [_i] * 3 + [ctypes.c_float, _vp]; lib.tw_rms_norm.restype = _i
     lib.tw_rms_norm_heads.argtypes = [_vp, _vp, _ll, _i, _ll, _ll, ctypes.c_float, _vp]; lib.tw_rms_norm_heads.restype = _i
+    lib.tw_rope_heads.argtypes = [_vp, _vp, _ll, _i, _ll, _ll, _vp, _vp, _ll, _i, _i, ctypes.c_float, _vp]; lib.tw_rope_heads.restype = _i
     lib.tw_gate_residual.argtypes = [_vp] * 3 + [_i] * 3 + [_vp]; lib.tw_gate_residual.restype = _i
     _lib = lib
     return lib
@@ -112,4 +113,4 @@ def check(status):
 EXPORTS = ('tw_status', 'tw_abi_version', 'tw_quantize_workspace', 'tw_quantize', 'tw_quantize_static',
            'tw_quantize_static_max_tiles', 'tw_swizzle_scales', 'tw_activation_rank', 'tw_selftest_bounded_wait',
            'tw_workspace', 'tw_fused', 'tw_fused_tile_n', 'tw_pack_rows', 'tw_select_tiles', 'tw_attention',
-           'tw_attention_workspace', 'tw_activate', 'tw_rms_norm', 'tw_rms_norm_heads', 'tw_gate_residual')
+           'tw_attention_workspace', 'tw_activate', 'tw_rms_norm', 'tw_rms_norm_heads', 'tw_rope_heads', 'tw_gate_residual')

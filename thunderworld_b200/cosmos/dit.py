@@ -27,6 +27,7 @@ class DiTConfig:
     blocks: int = 28
     head_dim: int = 128
     qk_norm: bool = True
+    rope: bool = True
     seed: int = 0
 
     def __post_init__(self):
@@ -46,6 +47,22 @@ class _Source:
     def __init__(self, weight):
         self.weight, self.bias = weight, None
         self.out_features, self.in_features = weight.shape
+
+
+def rope_tables(tokens, device, head_dim=128, theta=10000.0):
+    """cos / sin tables [tokens, head_dim] (float32) of a rotary position embedding over the token index; the two
+    halves of a head row rotate together (rotate-half convention of thunderworld_fp4/cosmos/pipeline_tuning.py:42-55)."""
+    inv = theta ** (-torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim)
+    ang = torch.arange(tokens, dtype=torch.float32)[:, None] * inv[None, :]
+    ang = torch.cat([ang, ang], -1)
+    return ang.cos().contiguous().to(device), ang.sin().contiguous().to(device)
+
+
+def apply_rope(x, cos, sin):
+    """Plain torch rotate-half RoPE in the dtype of x (reference arithmetic for tests)."""
+    d = x.shape[-1]
+    rot = torch.cat([-x[..., d // 2:], x[..., :d // 2]], -1)
+    return x * cos[:, None, :].to(x.dtype) + rot * sin[:, None, :].to(x.dtype)
 
 
 def rms_norm(x, eps=1e-6):
@@ -97,6 +114,13 @@ class DiTBlock(torch.nn.Module):
             return qkv_map
         return lambda ids: parallel.remap_tiles(ids, nb, kb, tp, r, split)
 
+    def controller_tables(self, tokens, device):
+        """Rotary tables of this sequence length, built once (before graph capture, in the warm-up pass)."""
+        cache = self.__dict__.setdefault('_rope', {})
+        if (tokens, device) not in cache:
+            cache[(tokens, device)] = rope_tables(tokens, device)
+        return cache[(tokens, device)]
+
     def _row_split(self, layer, x, stats=None):
         """Row-split linear: global activation factor, local GEMM, summed partial outputs.
         stats = (factor, max|x|) of the local shard when its producer reduced them."""
@@ -115,7 +139,13 @@ class DiTBlock(torch.nn.Module):
         y, f = ops.rms_norm(x, shift=shift1, scale=scale1, want_factor=True)
         qkv = self.qkv(y, factor=f).reshape(b, s, 3, self.local_heads, 128)
         q, k, v = qkv.unbind(2)
-        if self.cfg.qk_norm:
+        if self.cfg.rope:
+            # q/k head norm and rotary embedding in one pass over q and one over k (the reference's dataflow:
+            # q/k norm -> RoPE -> attention, thunderworld_fp4/cosmos/ar_cache.py:72-107)
+            cos, sin = self.controller_tables(s, x.device)
+            q = ops.rope_heads(q, cos, sin, norm=self.cfg.qk_norm)
+            k = ops.rope_heads(k, cos, sin, norm=self.cfg.qk_norm)
+        elif self.cfg.qk_norm:
             q, k = ops.rms_norm_heads(q), ops.rms_norm_heads(k)
         a = self.controller.attend(self.index, q, k, v).reshape(b, s, self.local_heads * 128)
         ops.gate_residual_(x, gate1, self._row_split(self.out, a))

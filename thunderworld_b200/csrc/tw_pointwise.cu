@@ -8,6 +8,8 @@
 //   tw_rms_norm       RMSNorm with optional weight (cosmos/norm_fusion.py:23-43) and optional AdaLN
 //                     modulation y = norm * (1 + scale[b]) + shift[b]
 //   tw_rms_norm_heads RMSNorm over head_dim = 128 rows of a strided [tokens, heads, 128] view (q / k norm)
+//   tw_rope_heads     exact-rounding rotary embedding of such rows (cosmos/pipeline_tuning.py:42-63), optionally
+//                     after the head norm in the same pass
 //   tw_gate_residual  x += gate[b] * y
 //
 // All are HBM-bound: 16-byte loads and stores, every input element read once. The factor is finished by the
@@ -164,16 +166,22 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const uint4* __restrict__
   }
 }
 
-// ---- RMSNorm over 128-wide head rows of a strided view: 8 lanes per row, 32 rows per CTA ------------
-__global__ void __launch_bounds__(256) rms_norm_heads_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
-                                                             long long rows, int heads, long long stride_token,
-                                                             long long stride_head, float eps) {
+// ---- RMSNorm and / or rotary embedding over 128-wide head rows of a strided view: 8 lanes per row, 32 rows per CTA
+// RoPE follows the reference's exact-rounding kernel (thunderworld_fp4/cosmos/pipeline_tuning.py:42-55):
+// y[d] = bf16( bf16(x[d] c[d]) + bf16(rot[d] s[d]) ), rot[d] = -x[d + 64] for d < 64, x[d - 64] otherwise, with
+// x the bf16 output of the norm when both run here (the same roundings as two separate kernels, one pass less).
+// A lane holds 16 consecutive channels, so its rotation partners sit in lane ^ 4 at the same positions.
+template <bool NORM, bool ROPE, typename TableT>
+__global__ void __launch_bounds__(256) head_rows_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                                                        long long rows, int heads, long long stride_token,
+                                                        long long stride_head, float eps, const TableT* __restrict__ cos_t,
+                                                        const TableT* __restrict__ sin_t, long long table_rows) {
   const long long row = (long long)blockIdx.x * 32 + (threadIdx.x >> 3);      // row = token * heads + head
   const int lane8 = threadIdx.x & 7;
   float v[16];
   const bool live = row < rows;
+  const long long token = live ? row / heads : 0, head = live ? row % heads : 0;
   if (live) {
-    const long long token = row / heads, head = row % heads;
     const uint4* src = reinterpret_cast<const uint4*>(x + token * stride_token + head * stride_head + lane8 * 16);
     float lo[8], hi[8];
     unpack8(__ldg(src), lo);
@@ -184,16 +192,33 @@ __global__ void __launch_bounds__(256) rms_norm_heads_kernel(const __nv_bfloat16
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = 0.f;
   }
-  float ss = 0.f;
+  if (NORM) {
+    float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) ss = __fmaf_rn(v[i], v[i], ss);
+    for (int i = 0; i < 16; ++i) ss = __fmaf_rn(v[i], v[i], ss);
 #pragma unroll
-  for (int o = 1; o < 8; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  const float rstd = rsqrtf(ss * (1.f / 128.f) + eps);
+    for (int o = 1; o < 8; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rstd = rsqrtf(ss * (1.f / 128.f) + eps);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = ROPE ? __bfloat162float(__float2bfloat16_rn(v[i] * rstd)) : v[i] * rstd;
+  }
+  if (ROPE) {
+    const long long t = (token % table_rows) * 128 + lane8 * 16;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float partner = __shfl_xor_sync(0xffffffffu, v[i], 4);
+      const float rot = lane8 < 4 ? -partner : partner;
+      float c = 0.f, sn = 0.f;
+      if (live) { c = (float)cos_t[t + i]; sn = (float)sin_t[t + i]; }
+      const float pc = __bfloat162float(__float2bfloat16_rn(__fmul_rn(v[i], c)));
+      const float qs = __bfloat162float(__float2bfloat16_rn(__fmul_rn(rot, sn)));
+      v[i] = __fadd_rn(pc, qs);
+    }
+  }
   if (live) {
     float lo[8], hi[8], unused = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { lo[i] = v[i] * rstd; hi[i] = v[8 + i] * rstd; }
+    for (int i = 0; i < 8; ++i) { lo[i] = v[i]; hi[i] = v[8 + i]; }
     uint4* dst = reinterpret_cast<uint4*>(y + row * 128 + lane8 * 16);
     dst[0] = pack8(lo, unused);
     dst[1] = pack8(hi, unused);
@@ -268,8 +293,31 @@ extern "C" int tw_rms_norm_heads(const void* x, void* y, long long tokens, int h
   if (!x || !y || tokens <= 0 || heads <= 0) return TW_ERR_ARGUMENT;
   if (misaligned(x) || misaligned(y) || ((stride_token | stride_head) & 7)) return TW_ERR_ALIGNMENT;
   const long long rows = tokens * heads;
-  rms_norm_heads_kernel<<<(unsigned)((rows + 31) / 32), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), rows, heads, stride_token, stride_head, eps);
+  head_rows_kernel<true, false, float><<<(unsigned)((rows + 31) / 32), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), rows, heads, stride_token, stride_head, eps,
+      nullptr, nullptr, 1);
+  return cudaGetLastError() == cudaSuccess ? TW_OK : TW_ERR_LAUNCH;
+}
+
+extern "C" int tw_rope_heads(const void* x, void* y, long long tokens, int heads, long long stride_token, long long stride_head,
+                             const void* cos_table, const void* sin_table, long long table_rows, int table_is_bf16, int norm,
+                             float eps, void* stream_) {
+  if (!x || !y || !cos_table || !sin_table || tokens <= 0 || heads <= 0 || table_rows <= 0) return TW_ERR_ARGUMENT;
+  if (misaligned(x) || misaligned(y) || ((stride_token | stride_head) & 7)) return TW_ERR_ALIGNMENT;
+  const long long rows = tokens * heads;
+  const unsigned grid = (unsigned)((rows + 31) / 32);
+  cudaStream_t st = static_cast<cudaStream_t>(stream_);
+  const __nv_bfloat16* xi = static_cast<const __nv_bfloat16*>(x);
+  __nv_bfloat16* yo = static_cast<__nv_bfloat16*>(y);
+  if (table_is_bf16) {
+    const __nv_bfloat16 *c = static_cast<const __nv_bfloat16*>(cos_table), *sn = static_cast<const __nv_bfloat16*>(sin_table);
+    if (norm) head_rows_kernel<true, true, __nv_bfloat16><<<grid, 256, 0, st>>>(xi, yo, rows, heads, stride_token, stride_head, eps, c, sn, table_rows);
+    else head_rows_kernel<false, true, __nv_bfloat16><<<grid, 256, 0, st>>>(xi, yo, rows, heads, stride_token, stride_head, eps, c, sn, table_rows);
+  } else {
+    const float *c = static_cast<const float*>(cos_table), *sn = static_cast<const float*>(sin_table);
+    if (norm) head_rows_kernel<true, true, float><<<grid, 256, 0, st>>>(xi, yo, rows, heads, stride_token, stride_head, eps, c, sn, table_rows);
+    else head_rows_kernel<false, true, float><<<grid, 256, 0, st>>>(xi, yo, rows, heads, stride_token, stride_head, eps, c, sn, table_rows);
+  }
   return cudaGetLastError() == cudaSuccess ? TW_OK : TW_ERR_LAUNCH;
 }
 

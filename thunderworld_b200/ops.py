@@ -277,6 +277,27 @@ def rms_norm_heads(x, eps=1e-6):
     return y
 
 
+def rope_heads(x, cos, sin, *, norm=False, eps=1e-6):
+    """Rotary embedding of a (possibly strided) bf16 view [..., tokens, heads, 128] with the reference's rounding
+    sequence (fused_rope, thunderworld_fp4/cosmos/pipeline_tuning.py:57-63); cos / sin [table_rows, 128], float32 or
+    bf16, row token % table_rows. norm=True runs the head RMSNorm first in the same pass. Returns a contiguous tensor."""
+    if x.dtype != torch.bfloat16 or not x.is_cuda or x.shape[-1] != 128 or x.stride(-1) != 1:
+        raise ValueError('expected a CUDA BF16 view [..., heads, 128] with unit inner stride')
+    if cos.shape != sin.shape or cos.ndim != 2 or cos.shape[1] != 128 or cos.dtype != sin.dtype or \
+            cos.dtype not in (torch.float32, torch.bfloat16) or not cos.is_contiguous() or not sin.is_contiguous():
+        raise ValueError('cos / sin must be contiguous [rows, 128] tables of one dtype (float32 or bfloat16)')
+    require_sm100(x.device)
+    heads = x.shape[-2]
+    lead = x.reshape(-1, heads, 128) if x.dim() != 3 else x
+    if lead.data_ptr() != x.data_ptr():
+        raise ValueError('leading dimensions must fold into one token stride')
+    y = torch.empty(x.shape, device=x.device, dtype=x.dtype)
+    _lib.check(_lib.load().tw_rope_heads(_ptr(lead), _ptr(y), lead.shape[0], heads, lead.stride(0), lead.stride(1), _ptr(cos),
+                                         _ptr(sin), cos.shape[0], int(cos.dtype == torch.bfloat16), int(norm), float(eps),
+                                         _stream(x.device)))
+    return y
+
+
 def gate_residual_(x, gate, y):
     """x += gate[:, None, :] * y in place; x, y [batch, tokens, hidden], gate [batch, hidden]."""
     _check_bf16(x, gate, y)
