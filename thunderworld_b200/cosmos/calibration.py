@@ -63,7 +63,7 @@ def quantize_weight(weight, prescale, *, base=1., residual=1., remove=None):
     `remove` (outlier proposal) are zeroed in the base plane only, so the residual plane carries them whole."""
     w = (weight.float() / prescale).bfloat16().float()
     peak = w.abs().amax()
-    factor = torch.where(peak > 0, peak / 2688., torch.ones_like(peak))
+    factor = torch.where(peak > 0, peak / torch.full_like(peak, 2688.), torch.ones_like(peak))   # tensor divisor: IEEE division on any device
     z = w / factor
     c0, s0 = _encode(z if remove is None else z.masked_fill(remove, 0.), base)
     c1, s1 = _encode(z - decode(c0, s0, torch.ones_like(factor)), residual)

@@ -114,13 +114,27 @@ def allreduce_sum(x, topo):
     return x
 
 
+_DIVISOR = {}
+
+
+def factor_of_peak(peak):
+    """max|x| -> max|x| / 2688 (1.0 for zero) with an IEEE division. The divisor is a tensor on purpose: torch
+    turns division of a CUDA tensor by a Python number into a multiplication by the rounded reciprocal, which
+    is off by one ulp for some peaks and would make a shard's packed bytes differ from the unsharded
+    quantizer's (which divides)."""
+    key = (peak.device, peak.dtype)
+    if key not in _DIVISOR:
+        _DIVISOR[key] = torch.full((1,), 2688., device=peak.device, dtype=peak.dtype)
+    return torch.where(peak > 0, peak / _DIVISOR[key], torch.ones_like(peak)).reshape(())
+
+
 def global_factor(x_local, topo):
     """Tensor-wide NVFP4 factor max|x| / 2688 (1.0 for an all-zero tensor) of an activation whose K
     dimension is divided over the tensor-parallel group: one 4-byte MAX all-reduce."""
     peak = x_local.abs().amax().float().reshape(1)
     if topo.tp_size > 1:
         dist.all_reduce(peak, op=dist.ReduceOp.MAX, group=topo.tp_group)
-    return torch.where(peak > 0, peak / 2688., torch.ones_like(peak)).reshape(())
+    return factor_of_peak(peak)
 
 
 def global_factor_from_peak(peak, topo):
@@ -128,7 +142,7 @@ def global_factor_from_peak(peak, topo):
     already reduced."""
     if topo.tp_size > 1:
         dist.all_reduce(peak, op=dist.ReduceOp.MAX, group=topo.tp_group)
-    return torch.where(peak > 0, peak / 2688., torch.ones_like(peak)).reshape(())
+    return factor_of_peak(peak)
 
 
 def guide(branch_output, scale, topo):
