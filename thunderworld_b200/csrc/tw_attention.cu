@@ -360,7 +360,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                  const __grid_constant__ CUtensorMap tm_v, const AttParams p) {
   using L = AttSmem;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // aligned by pointer arithmetic on the __shared__ array (not through an integer cast), so that the compiler
+  // keeps the address space and emits shared-memory loads and stores instead of generic ones
+  uint8_t* smem = smem_raw + ((1024u - (tw::smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* qFull = bars;
   uint64_t* kFull = qFull + 1;
@@ -586,29 +588,57 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tw::tc_fence_after();
       const float4* kf = reinterpret_cast<const float4*>(smem + L::OFF_KF + s * 512);
       const int n_valid = p.n - t * 128;                      // columns >= n_valid are padding
+      // Both passes walk the 128 scores of the row in K16 groups with the tensor-memory load of the next group
+      // in flight while the current one is processed (two 16-register buffers). The loads and their waits are
+      // ordered among themselves and tied to the destination registers, but are no barrier for other
+      // instructions: a thread runs long dependent chains (shared-memory load -> multiply -> exp2 -> convert ->
+      // pack), and with two softmax warps per scheduler the only way to hide their latency is to let the
+      // chains of neighbouring groups overlap. Arithmetic on pairs of columns uses the packed f32x2 forms,
+      // which round exactly like two scalar operations.
+      const uint32_t s_src = lane_base + TM_S + par * 128;
+      auto walk = [&](auto&& process, auto&& last_load_done) {
+        uint32_t va[16], vb[16];
+        tw::tmem_load_16_async(s_src, va);
+        tw::tmem_load_wait(va);
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          tw::tmem_load_16_async(s_src + c * 32 + 16, vb);
+          process(va, c, std::integral_constant<int, 0>{});
+          tw::tmem_load_wait(vb);
+          if (c < 3) tw::tmem_load_16_async(s_src + c * 32 + 32, va);
+          else last_load_done();
+          process(vb, c, std::integral_constant<int, 1>{});
+          if (c < 3) tw::tmem_load_wait(va);
+        }
+      };
+      // products S * kf of columns 4 i .. 4 i + 3 of a K16 group, as two pairs
+      auto scaled = [&](const uint32_t (&v)[16], int c, int g, int i, float2& e0, float2& e1) {
+        const float4 f = kf[c * 8 + g * 4 + i];
+        e0 = __fmul2_rn(make_float2(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1])), make_float2(f.x, f.y));
+        e1 = __fmul2_rn(make_float2(__uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3])), make_float2(f.z, f.w));
+      };
       // pass 1: maximum of S * kf per K16 group
       float rowmax = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tw::tmem_load_32x32(lane_base + TM_S + par * 128 + c * 32, v);
-        tw::tmem_load_wait();
+      walk([&](const uint32_t (&v)[16], int c, auto g_tag) {
+        constexpr int g = decltype(g_tag)::value;
+        float part[4];
 #pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          float best = -INFINITY;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float4 f = kf[c * 8 + g * 4 + i];
-            const float e[4] = {__uint_as_float(v[g * 16 + 4 * i]) * f.x, __uint_as_float(v[g * 16 + 4 * i + 1]) * f.y,
-                                __uint_as_float(v[g * 16 + 4 * i + 2]) * f.z, __uint_as_float(v[g * 16 + 4 * i + 3]) * f.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              best = fmaxf(best, (!TAIL || (c * 32 + g * 16 + 4 * i + j) < n_valid) ? e[j] : -INFINITY);
+        for (int i = 0; i < 4; ++i) {
+          float2 e0, e1;
+          scaled(v, c, g, i, e0, e1);
+          if (TAIL) {
+            const int col = c * 32 + g * 16 + 4 * i;
+            if (col >= n_valid) e0.x = -INFINITY;
+            if (col + 1 >= n_valid) e0.y = -INFINITY;
+            if (col + 2 >= n_valid) e1.x = -INFINITY;
+            if (col + 3 >= n_valid) e1.y = -INFINITY;
           }
-          gsm[(c * 2 + g) * 128 + r] = best;
-          rowmax = fmaxf(rowmax, best);
+          part[i] = fmaxf(fmaxf(e0.x, e0.y), fmaxf(e1.x, e1.y));
         }
-      }
+        const float best = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
+        gsm[(c * 2 + g) * 128 + r] = best;
+        rowmax = fmaxf(rowmax, best);
+      }, [] {});
       rowmax *= qfl;                                          // qfl > 0
       if (rowmax > ref + 8.f) ref = rowmax;                   // lazy reference
       const float off = fmaxf(rowmax - 10.584962500721156f, ref - 39.863137138648348f);
@@ -621,76 +651,91 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       uint8_t* sfp = smem + L::OFF_SFP + par * 2 * ATT_SF;
       float zsum = 0.f;
       uint32_t sf_base = 0u, sf_res = 0u;
+      uint32_t w[4], rw[4];
+      const float2 q2 = make_float2(qfl, qfl);
       // pass 2: per K16 group the E4M3 scale follows from the group maximum, and the codes are the E2M1
       // roundings of y = exp2(x - off - log2(scale)) = z / scale
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tw::tmem_load_32x32(lane_base + TM_S + par * 128 + c * 32, v);
-        tw::tmem_load_wait();
-        if (c == 3) {                                         // scores are in registers: release S[par]
-          tw::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) tw::mbar_arrive(sEmpty + par);
-        }
-        uint32_t w[4], rw[4];
+      // scale of a K16 group from its maximum: E4M3 byte, its value, and the exponent offset of the group. The
+      // chain (exp2 -> convert -> convert back -> log2) is long, so the one of the next group is started before
+      // the columns of the current group are processed.
+      float next_sv, next_offg;
+      uint32_t next_sb;
+      auto group_scale = [&](int group) {
+        const float peak = exp2_approx(__fmaf_rn(gsm[group * 128 + r], qfl, -off));
+        next_sb = tw::f32_to_e4m3(fmaxf(peak * (1.f / 6.f), 0.001953125f));
+        next_sv = tw::e4m3_to_f32(next_sb);
+        next_offg = off + lg2_approx(next_sv);
+      };
+      group_scale(0);
+      walk([&](const uint32_t (&v)[16], int c, auto g_tag) {
+        constexpr int g = decltype(g_tag)::value;
+        const uint32_t sb = next_sb;
+        const float sv = next_sv, offg = next_offg;
+        if (g == 0 || c < 3) group_scale(c * 2 + g + 1);
+        const float2 o2 = make_float2(-offg, -offg);
+        float2 y[8];
+        float2 ysum = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          const float peak = exp2_approx(__fmaf_rn(gsm[(c * 2 + g) * 128 + r], qfl, -off));
-          const uint32_t sb = tw::f32_to_e4m3(fmaxf(peak * (1.f / 6.f), 0.001953125f));
-          const float sv = tw::e4m3_to_f32(sb);
-          const float offg = off + lg2_approx(sv);
-          float y[16];
-          float ysum = 0.f;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float4 f = kf[c * 8 + g * 4 + i];
-            const float e[4] = {__uint_as_float(v[g * 16 + 4 * i]) * f.x, __uint_as_float(v[g * 16 + 4 * i + 1]) * f.y,
-                                __uint_as_float(v[g * 16 + 4 * i + 2]) * f.z, __uint_as_float(v[g * 16 + 4 * i + 3]) * f.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float yy = exp2_approx(__fmaf_rn(e[j], qfl, -offg));
-              if (TAIL && (c * 32 + g * 16 + 4 * i + j) >= n_valid) yy = 0.f;
-              y[4 * i + j] = yy;
-              ysum += yy;
-            }
+        for (int i = 0; i < 4; ++i) {
+          float2 e0, e1;
+          scaled(v, c, g, i, e0, e1);
+          e0 = __ffma2_rn(e0, q2, o2);
+          e1 = __ffma2_rn(e1, q2, o2);
+          y[2 * i] = make_float2(exp2_approx(e0.x), exp2_approx(e0.y));
+          y[2 * i + 1] = make_float2(exp2_approx(e1.x), exp2_approx(e1.y));
+          if (TAIL) {
+            const int col = c * 32 + g * 16 + 4 * i;
+            if (col >= n_valid) y[2 * i].x = 0.f;
+            if (col + 1 >= n_valid) y[2 * i].y = 0.f;
+            if (col + 2 >= n_valid) y[2 * i + 1].x = 0.f;
+            if (col + 3 >= n_valid) y[2 * i + 1].y = 0.f;
           }
-          zsum = __fmaf_rn(ysum, sv, zsum);
-          uint32_t b[8];
+          ysum = __fadd2_rn(ysum, __fadd2_rn(y[2 * i], y[2 * i + 1]));
+        }
+        zsum = __fmaf_rn(ysum.x + ysum.y, sv, zsum);
+        uint32_t b[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) b[i] = tw::f32x2_to_e2m1x2(y[2 * i], y[2 * i + 1]);
-          w[2 * g] = pack4(b[0], b[1], b[2], b[3]);
-          w[2 * g + 1] = pack4(b[4], b[5], b[6], b[7]);
-          sf_base |= sb << (8 * ((c & 1) * 2 + g));
-          if (REP) {
-            // residual in units of the base scale: res = y - value(code); its scale is sv * max|res| / 6
-            float rpeak = 0.f;
+        for (int i = 0; i < 8; ++i) b[i] = tw::f32x2_to_e2m1x2(y[i].x, y[i].y);
+        w[2 * g] = pack4(b[0], b[1], b[2], b[3]);
+        w[2 * g + 1] = pack4(b[4], b[5], b[6], b[7]);
+        sf_base |= sb << (8 * ((c & 1) * 2 + g));
+        if (REP) {
+          // residual in units of the base scale: res = y - value(code); its scale is sv * max|res| / 6
+          float rpeak = 0.f;
+          const float2 minus = make_float2(-1.f, -1.f);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float2 val = e2m1x2_values(b[i]);
-              y[2 * i] -= val.x;
-              y[2 * i + 1] -= val.y;
-              rpeak = fmaxf(rpeak, fmaxf(fabsf(y[2 * i]), fabsf(y[2 * i + 1])));
-            }
-            const uint32_t rsb = tw::f32_to_e4m3(fmaxf(rpeak * sv * (1.f / 6.f), 0.001953125f));
-            const float mult = sv * rcp_approx(tw::e4m3_to_f32(rsb));
+          for (int i = 0; i < 8; ++i) {
+            y[i] = __ffma2_rn(e2m1x2_values(b[i]), minus, y[i]);
+            rpeak = fmaxf(rpeak, fmaxf(fabsf(y[i].x), fabsf(y[i].y)));
+          }
+          const uint32_t rsb = tw::f32_to_e4m3(fmaxf(rpeak * sv * (1.f / 6.f), 0.001953125f));
+          const float mult = sv * rcp_approx(tw::e4m3_to_f32(rsb));
+          const float2 m2 = make_float2(mult, mult);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) b[i] = tw::f32x2_to_e2m1x2(y[2 * i] * mult, y[2 * i + 1] * mult);
-            rw[2 * g] = pack4(b[0], b[1], b[2], b[3]);
-            rw[2 * g + 1] = pack4(b[4], b[5], b[6], b[7]);
-            sf_res |= rsb << (8 * ((c & 1) * 2 + g));
+          for (int i = 0; i < 8; ++i) {
+            const float2 scaled_res = __fmul2_rn(y[i], m2);
+            b[i] = tw::f32x2_to_e2m1x2(scaled_res.x, scaled_res.y);
+          }
+          rw[2 * g] = pack4(b[0], b[1], b[2], b[3]);
+          rw[2 * g + 1] = pack4(b[4], b[5], b[6], b[7]);
+          sf_res |= rsb << (8 * ((c & 1) * 2 + g));
+        }
+        if (g == 1) {
+          // K16 groups 2c and 2c + 1 of a row share one 16-byte chunk of the 64-byte-swizzled P tile
+          const uint32_t code_off = (uint32_t)r * 64u + (uint32_t)((c ^ ((r >> 1) & 3)) << 4);
+          *reinterpret_cast<uint4*>(p0 + code_off) = make_uint4(w[0], w[1], w[2], w[3]);
+          if (REP) *reinterpret_cast<uint4*>(p0 + ATT_TILE + code_off) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+          if (c & 1) {                                        // four scale bytes of the row: one word of the atom layout
+            *reinterpret_cast<uint32_t*>(sfp + atom_offset(r, (c >> 1) * 4)) = sf_base;
+            if (REP) *reinterpret_cast<uint32_t*>(sfp + ATT_SF + atom_offset(r, (c >> 1) * 4)) = sf_res;
+            sf_base = sf_res = 0u;
           }
         }
-        // K16 groups 2c and 2c + 1 of a row share one 16-byte chunk of the 64-byte-swizzled P tile
-        const uint32_t code_off = (uint32_t)r * 64u + (uint32_t)((c ^ ((r >> 1) & 3)) << 4);
-        *reinterpret_cast<uint4*>(p0 + code_off) = make_uint4(w[0], w[1], w[2], w[3]);
-        if (REP) *reinterpret_cast<uint4*>(p0 + ATT_TILE + code_off) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
-        if (c & 1) {                                          // four scale bytes of the row: one word of the atom layout
-          *reinterpret_cast<uint32_t*>(sfp + atom_offset(r, (c >> 1) * 4)) = sf_base;
-          if (REP) *reinterpret_cast<uint32_t*>(sfp + ATT_SF + atom_offset(r, (c >> 1) * 4)) = sf_res;
-          sf_base = sf_res = 0u;
-        }
-      }
+      }, [&] {                                                // all scores are in registers: release S[par]
+        tw::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tw::mbar_arrive(sEmpty + par);
+      });
       stats[(t & 3) * 128 + r] = make_float4(ref, pf, zsum * pf, 0.f);
       // P visible to the tensor core (async proxy); key factors consumed
       tw::fence_proxy_async();

@@ -172,7 +172,9 @@ fused_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                   const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1, const PairParams p) {
   using C = PairCfg;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // aligned by pointer arithmetic on the __shared__ array (not through an integer cast), so that the compiler
+  // keeps the address space and emits shared-memory loads and stores instead of generic ones
+  uint8_t* smem = smem_raw + ((1024u - (tw::smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint64_t* fullS = bars;                       // a step's operands have landed (leader: in both CTAs)
   uint64_t* emptyS = fullS + C::STAGES;         // the MMAs that read the base stage have completed
