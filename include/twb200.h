@@ -111,6 +111,12 @@ typedef struct TwRepairIO {
                               block (explicit masks of FP4Linear, thunderworld_fp4/linear.py:115-119) */
   int32_t kernel;          /* 0: the library chooses (today: the single-CTA kernel); 1: single-CTA kernel; 2: CTA-pair kernel (cta_group::2;
                               needs n % 256 == 0, m > 128 and no mask_per_n). Both give the same bits. */
+  int32_t activation;      /* 0: none. TW_ACT_GELU_TANH: out = bf16(gelu_tanh(bf16(alpha * acc + bias))), bit for bit what
+                              tw_activate produces from this call's plain output (the FFN-up projection followed by
+                              activate_with_factor, thunderworld_fp4/_fusion.py:26-34, in one pass; single-CTA kernel only) */
+  float* stats;            /* with an activation, optional: {max|out| / 2688 (1 for an all-zero out), max|out|} over the m x n
+                              output, written by the last CTA to finish */
+  uint32_t* stats_scratch; /* two zeroed words (required with stats); left zeroed */
 } TwRepairIO;
 /* Limits: n % 128 == 0, k % 128 == 0, k <= 24576 (else the "size exceeds the stated maximum" status).
  * Bytes of caller-owned workspace (holds the device status word; zero it once). */

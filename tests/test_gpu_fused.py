@@ -180,3 +180,39 @@ def test_mask_is_read_at_run_time_under_graph_replay():
     torch.cuda.synchronize()
     eager = op(new_x)
     assert torch.equal(out, eager)
+
+
+@pytest.mark.parametrize('m,n,k,a_fraction,w_fraction,with_bias', [
+    (300, 512, 512, 0.5, 0.5, True),        # M tail: rows beyond m (gelu(bias) != 0 there) must not reach the maximum
+    (256, 384, 512, 0.0, 0.0, False),       # 128-wide tiles
+    (1000, 1024, 1024, 0.5, 0.25, False),   # several tiles per CTA
+])
+def test_fused_activation_epilogue_matches_the_separate_activation_pass(m, n, k, a_fraction, w_fraction, with_bias):
+    """GELU in the GEMM epilogue = activate_with_factor applied to the plain GEMM output, bit for bit, and the
+    (factor, max) pair equals the one the separate pass reduces."""
+    from thunderworld_b200 import ops
+    op, x, _, am, _ = build(m, n, k, 11, a_fraction, w_fraction)
+    bias = (torch.randn(n, generator=torch.Generator().manual_seed(1)) * 0.5).bfloat16().cuda() if with_bias else None
+    packed = op.pack(x)
+    plain = op.run_packed(x, packed, bias=bias)
+    want, want_stats = ops.activate_with_factor(plain, mode='gelu_tanh', return_stats=True)
+    got, stats = op.run_packed(x, packed, bias=bias, activation='gelu_tanh', want_stats=True)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    assert torch.equal(stats, want_stats), (stats, want_stats)
+    again, stats2 = op.run_packed(x, packed, bias=bias, activation='gelu_tanh', want_stats=True)   # scratch was left zeroed
+    assert torch.equal(stats2, want_stats) and torch.equal(again, got)
+    only = op.run_packed(x, packed, bias=bias, activation='gelu_tanh')                              # without the reduction
+    assert torch.equal(only, got)
+    assert ops.device_status() == 0
+
+
+def test_fused_activation_argument_checks():
+    op, x, _, _, _ = build(256, 512, 512, 3, 0.0, 0.0)
+    packed = op.pack(x)
+    with pytest.raises(ValueError):
+        op.run_packed(x, packed, activation='relu2')
+    with pytest.raises(ValueError):
+        op.run_packed(x, packed, want_stats=True)
+    op.kernel = 2                                            # the CTA-pair kernel has no activation epilogue
+    with pytest.raises(RuntimeError):
+        op.run_packed(x, packed, activation='gelu_tanh')

@@ -27,7 +27,8 @@ class RepairIO(ctypes.Structure):
     """Reference RepairIO (cutlass/backend.py:10-12) + bank_blocks + atom-layout residual scales."""
     _fields_ = [(n, _vp) for n in ('ac', 'ascale', 'wc', 'ws', 'wr', 'wrs', 'wi', 'off', 'wloc', 'mask')] + \
                [(n, _i) for n in ('m', 'mp', 'n', 'k', 'na', 'hasw', 'cross', 'shared', 'dense', 'bank_blocks')] + \
-               [(n, _vp) for n in ('a1s_swz', 'wrs_swz', 'bias')] + [('mask_per_n', _i), ('kernel', _i)]
+               [(n, _vp) for n in ('a1s_swz', 'wrs_swz', 'bias')] + [('mask_per_n', _i), ('kernel', _i), ('activation', _i),
+                ('stats', _vp), ('stats_scratch', _vp)]
 
 
 _ll = ctypes.c_longlong

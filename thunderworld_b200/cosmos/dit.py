@@ -150,7 +150,7 @@ class DiTBlock(torch.nn.Module):
         a = self.controller.attend(self.index, q, k, v).reshape(b, s, self.local_heads * 128)
         ops.gate_residual_(x, gate1, self._row_split(self.out, a))
         y, f = ops.rms_norm(x, shift=shift2, scale=scale2, want_factor=True)
-        u, stats = ops.activate_with_factor(self.up(y, factor=f), mode='gelu_tanh', return_stats=True)
+        u, stats = self.up(y, factor=f, activation='gelu_tanh')      # GELU and max|u| come out of the GEMM epilogue
         return ops.gate_residual_(x, gate2, self._row_split(self.down, u, stats))
 
 

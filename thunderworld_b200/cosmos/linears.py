@@ -114,7 +114,7 @@ class RepairLinear(torch.nn.Module):
         self.ops[key] = op
         self.bound = op
 
-    def _compute(self, x, factor=None, packed=None):
+    def _compute(self, x, factor=None, packed=None, activation=None):
         op = self.bound
         m, k = x.shape
         kb = k // 128
@@ -134,9 +134,11 @@ class RepairLinear(torch.nn.Module):
                 use_factor = factor if (base, res) == (1., 1.) else None
                 packed = ops.quantize(x, d, repair=mode, mask=op.am if mode == 2 else None, factor=use_factor, **common)
         # the bias is added in fp32 before the single bf16 rounding of the epilogue (TwRepairIO.bias)
-        return op.run_packed(x, packed, bias=self.bias)
+        return op.run_packed(x, packed, bias=self.bias, activation=activation, want_stats=activation is not None)
 
-    def forward(self, x, *, factor=None, packed=None):
+    def forward(self, x, *, factor=None, packed=None, activation=None):
+        """activation='gelu_tanh': the activation is applied in the GEMM epilogue and the call returns
+        (y, stats) with stats = (max|y| / 2688, max|y|), as ops.activate_with_factor(..., return_stats=True) would."""
         shape = x.shape
         flat = x.reshape(-1, self.in_features).contiguous()
         c = self.controller
@@ -149,4 +151,7 @@ class RepairLinear(torch.nn.Module):
             raise RuntimeError(f'Unwarmed projection {self.name}: {key}')
         else:
             self.bound = self.ops[key]
+        if activation is not None:
+            y, stats = self._compute(flat, factor, packed, activation)
+            return y.reshape(*shape[:-1], self.out_features), stats
         return self._compute(flat, factor, packed).reshape(*shape[:-1], self.out_features)

@@ -19,7 +19,7 @@ extern "C" const char* tw_status(int status) {
   }
 }
 
-extern "C" int tw_abi_version(void) { return 2; }
+extern "C" int tw_abi_version(void) { return 3; }
 
 // ---------------------------------------------------------------------------------------------
 // Self-test of the bounded-wait protocol every kernel of this library uses: one warp waits on a barrier

@@ -51,6 +51,14 @@ __device__ __forceinline__ uint32_t f32x2_to_e2m1x2(float lo, float hi) {
   asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %2, %1; cvt.u32.u8 %0, t; }" : "=r"(r) : "f"(lo), "f"(hi));
   return r;
 }
+// tanh-form GELU in fp32 (tanh.approx), shared by the pointwise activation kernel and the GEMM epilogue so that
+// both produce the same bits.
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float u = 0.7978845608028654f * __fmaf_rn(0.044715f * x, x * x, x);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  return 0.5f * x * (1.f + t);
+}
 // ---------------------------------------------------------------------------
 // Shared-memory addresses, mbarriers
 // ---------------------------------------------------------------------------

@@ -101,6 +101,9 @@ struct Params {
   int m, mp, n, k, na, hasw, cross, shared, dense;
   int kb, nb, mb, tiles_n, tiles;
   int mask_per_n;           // mask is [MB, NB, KB] (one A support per output block; 128-wide tiles only)
+  int act;                  // nonzero: tanh-form GELU of the bf16-rounded result, rounded to bf16 again
+  float* stats;             // with act, optional: {max|out| / 2688, max|out|}
+  unsigned* scratch;        // two zeroed words: running maximum (float bits), CTA ticket
 };
 
 // Per-tile term table, built ahead of use by its own warp: one bit per kb for "A1 selected" and
@@ -446,6 +449,7 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
     uint8_t* stage = smem + C::OFF_EPI + (warp - C::FIRST_EPI_WARP) * 4096;
     uint8_t* my_row = stage + lane * 128;
     uint32_t it = 0;
+    float peak = 0.f;                                       // max |activated output| of this lane's rows (rows < m only)
     for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++it) {
       const int mbi = tile / p.tiles_n, nt = tile % p.tiles_n;
       const uint32_t a = it & 1;
@@ -455,6 +459,7 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
       const int row0 = mbi * 128 + quad * 32;
       const int col = nt * BN + group * C::EPI_COLS;
       const bool live = col < p.n;                          // 128 columns of a 256-wide kernel never happen; kept for safety
+      const bool in_m = row0 + lane < p.m;                  // rows beyond m are clipped by the store and excluded from the maximum
       // 64 columns per round: two back-to-back TMEM loads, one wait. Accumulator 0 shares its last 64
       // columns with accumulator 1's first 64, so the rounds of accumulator 0 run backwards: the shared
       // columns are read first and the MMA issuer is told before they are converted and stored.
@@ -488,6 +493,11 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
               const float lo = __fmaf_rn(__uint_as_float(r[part][8 * v + 2 * q]), alpha, tw::bf16_bits_to_float(bw[q] & 0xffffu));
               const float hi = __fmaf_rn(__uint_as_float(r[part][8 * v + 2 * q + 1]), alpha, tw::bf16_bits_to_float(bw[q] >> 16));
               __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
+              if (p.act) {
+                // the activation sees the bf16 value an unfused call would have stored, and is rounded once more
+                b2 = __floats2bfloat162_rn(tw::gelu_tanh(__low2float(b2)), tw::gelu_tanh(__high2float(b2)));
+                if (in_m) peak = fmaxf(peak, fmaxf(fabsf(__low2float(b2)), fabsf(__high2float(b2))));
+              }
               w[q] = *reinterpret_cast<uint32_t*>(&b2);
             }
             const int chunk = part * 4 + v;                 // 16-byte chunk of the 128-byte row; swizzled by the row
@@ -500,11 +510,28 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
       }
     }
     if (lane == 0) tw::bulk_store_wait_all();               // global writes are complete before the CTA exits
+    if (p.act && p.stats) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, o));
+      // the bit pattern of a non-negative float orders like the float
+      if (lane == 0) { atomicMax(p.scratch, __float_as_uint(peak)); __threadfence(); }
+    }
   }
 
   tw::tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, TW_ERR_TIMEOUT);
+  if (threadIdx.x == 0 && p.act && p.stats) {
+    // the last CTA to take a ticket publishes the tensor factor and clears the scratch for the next call
+    __threadfence();
+    if (atomicAdd(p.scratch + 1, 1u) == gridDim.x - 1) {
+      __threadfence();
+      const float top = __uint_as_float(atomicExch(p.scratch, 0u));
+      p.stats[0] = top > 0.f ? __fdiv_rn(top, 2688.f) : 1.f;
+      p.stats[1] = top;
+      p.scratch[1] = 0u;
+    }
+  }
   if (warp == 1) { tw::tc_fence_after(); tw::tmem_dealloc(*tmem_slot, C::TM_COLS); }
 }
 
@@ -585,6 +612,7 @@ int launch(int m, int n, int k, const void* a_codes, const void* w_codes, const 
   p.status = static_cast<int*>(workspace);
   p.m = m; p.mp = io->mp; p.n = n; p.k = k; p.na = io->na; p.hasw = io->hasw; p.cross = io->cross;
   p.shared = io->shared; p.dense = io->dense; p.mask_per_n = io->mask_per_n;
+  p.act = io->activation; p.stats = io->stats; p.scratch = io->stats_scratch;
   p.kb = k / 128; p.nb = n / 128; p.mb = (m + 127) / 128;
   p.tiles_n = (n + BN - 1) / BN;
   p.tiles = p.mb * p.tiles_n;
@@ -638,6 +666,8 @@ extern "C" int tw_fused(int m, int n, int k, const void* a_codes, const void* w_
   if (major != 10) return TW_ERR_ARCH;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (io->kernel < 0 || io->kernel > 3) return TW_ERR_ARGUMENT;
+  if (io->activation != 0 && io->activation != TW_ACT_GELU_TANH) return TW_ERR_ARGUMENT;
+  if ((io->stats && (!io->activation || !io->stats_scratch)) || (io->activation && io->kernel == 2)) return TW_ERR_ARGUMENT;
   // 256-wide tiles on CTA pairs (two row blocks per tile) unless the caller asks for the single-CTA kernel
   const bool pair_ok = n % 256 == 0 && !io->mask_per_n && m > 128;
   if (io->kernel == 2 && !pair_ok) return TW_ERR_SHAPE;

@@ -78,12 +78,7 @@ __device__ __forceinline__ void finish_factor(float peak, unsigned* scratch, flo
   }
 }
 
-__device__ __forceinline__ float gelu_tanh(float x) {
-  const float u = 0.7978845608028654f * __fmaf_rn(0.044715f * x, x * x, x);
-  float t;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
-  return 0.5f * x * (1.f + t);
-}
+using tw::gelu_tanh;
 
 // ---- activation -----------------------------------------------------------------------------
 template <int MODE>

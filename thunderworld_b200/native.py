@@ -73,7 +73,7 @@ class Native:
         repair = 0 if self.na == 0 else (1 if self.na == self.k // 128 else 2)
         return ops.quantize(x, self.d, repair=repair, mask=self.union if repair == 2 else None, wg=self.wg, **kw)
 
-    def run_packed(self, x, packed, out=None, bias=None):
+    def run_packed(self, x, packed, out=None, bias=None, activation=None, want_stats=False):
         m = x.shape[0]
         self._refresh_bank()
         if not isinstance(packed, ops.Packed):
@@ -82,7 +82,7 @@ class Native:
                               mask=self.am, wr=self.wr if self.hasw else None, wrs_swz=self.wrs_swz, wi=self.wi,
                               off=self.off, wloc=self.wloc, cross=self.cross, shared=self.shared_bank,
                               dense=self.dense_w, ws=self.ws, wrs=self.wrs if self.hasw else None, out=out,
-                              kernel=getattr(self, 'kernel', 0), bias=bias)
+                              kernel=getattr(self, 'kernel', 0), bias=bias, activation=activation, want_stats=want_stats)
 
     def __call__(self, x):
         if x.ndim != 2 or x.shape[1] != self.k or x.shape[0] <= 0 or ops.cdiv(x.shape[0], 128) != self.am.shape[0]:

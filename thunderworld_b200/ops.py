@@ -148,8 +148,10 @@ def selftest_bounded_wait(device=None, limit_cycles=2_000_000):
 
 def fused_gemm(m, n, k, packed, wc, ws_swz, alpha, *, na=0, mask=None, wr=None, wrs_swz=None, wi=None, off=None,
                wloc=None, cross=False, shared=False, dense=False, ws=None, wrs=None, out=None, workspace=None,
-               mask_per_n=False, bias=None, kernel=0):
-    """One launch of the repaired GEMM; returns bf16 [m,n]."""
+               mask_per_n=False, bias=None, kernel=0, activation=None, want_stats=False):
+    """One launch of the repaired GEMM; returns bf16 [m,n]. activation='gelu_tanh' applies the activation to the
+    bf16-rounded result in the epilogue (the bits activate_with_factor would give); with want_stats the call returns
+    (out, stats) with stats = float32 [2] = (max|out| / 2688, max|out|)."""
     lib = _lib.load()
     dev = wc.device
     require_sm100(dev)
@@ -164,11 +166,21 @@ def fused_gemm(m, n, k, packed, wc, ws_swz, alpha, *, na=0, mask=None, wr=None, 
                        _ptr(wrs) if hasw else None, _ptr(wi), _ptr(off), _ptr(wloc), _ptr(mask),
                        m, packed.mp, n, k, int(na), int(hasw), int(cross), int(shared), int(dense),
                        int(wr.shape[0]) if hasw else 0, _ptr(a1s) if na else None, _ptr(wrs_swz) if hasw else None,
-                       _ptr(bias), int(mask_per_n), int(kernel))
+                       _ptr(bias), int(mask_per_n), int(kernel), 0, None, None)
+    stats = None
+    if activation is not None:
+        if activation != 'gelu_tanh':
+            raise ValueError('the GEMM epilogue fuses gelu_tanh only')
+        io.activation = ACT_MODES[activation]
+        if want_stats:
+            stats, scratch = _stats(dev, True)
+            io.stats, io.stats_scratch = _ptr(stats), _ptr(scratch)
+    elif want_stats:
+        raise ValueError('stats come with a fused activation')
     with torch.cuda.device(dev):
         _lib.check(lib.tw_fused(m, n, k, packed.codes.data_ptr(), wc.data_ptr(), a0s.data_ptr(), ws_swz.data_ptr(),
                                 out.data_ptr(), alpha.data_ptr(), workspace.data_ptr(), _stream(dev), ctypes.byref(io)))
-    return out
+    return (out, stats) if want_stats else out
 
 
 STATUS_KEYS = {'g': 0, 'a': 0, 'q': 8}   # workspace -> byte offset of its device status word: fused GEMM, attention, quantizer
