@@ -781,34 +781,48 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const bool keep = __all_sync(0xffffffffu, alpha == 1.f);
       tw::tc_fence_after();
       const float4* vf = reinterpret_cast<const float4*>(smem + L::OFF_VF + s * 512) + (c0 >> 2);
+      // T is read 16 columns at a time with the next load in flight; the T buffer is handed back to the MMA warp
+      // as soon as the last load has landed, before the last columns are accumulated. Pairs of channels use the
+      // packed f32x2 forms (same rounding as two scalar operations).
+      const float2 pf2 = make_float2(pf, pf), alpha2 = make_float2(alpha, alpha);
+      auto accumulate = [&](const uint32_t (&v)[16], int c) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[16];
-        tw::tmem_load_32x32_x16(lane_base + TM_T + c0 + c * 16, v);
-        tw::tmem_load_wait();
-        if (keep) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float4 f = vf[c * 4 + i];
-            acc[c * 16 + 4 * i + 0] = __fmaf_rn(__uint_as_float(v[4 * i + 0]) * f.x, pf, acc[c * 16 + 4 * i + 0]);
-            acc[c * 16 + 4 * i + 1] = __fmaf_rn(__uint_as_float(v[4 * i + 1]) * f.y, pf, acc[c * 16 + 4 * i + 1]);
-            acc[c * 16 + 4 * i + 2] = __fmaf_rn(__uint_as_float(v[4 * i + 2]) * f.z, pf, acc[c * 16 + 4 * i + 2]);
-            acc[c * 16 + 4 * i + 3] = __fmaf_rn(__uint_as_float(v[4 * i + 3]) * f.w, pf, acc[c * 16 + 4 * i + 3]);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float4 f = vf[c * 4 + i];
-            acc[c * 16 + 4 * i + 0] = __fmaf_rn(__uint_as_float(v[4 * i + 0]) * f.x, pf, acc[c * 16 + 4 * i + 0] * alpha);
-            acc[c * 16 + 4 * i + 1] = __fmaf_rn(__uint_as_float(v[4 * i + 1]) * f.y, pf, acc[c * 16 + 4 * i + 1] * alpha);
-            acc[c * 16 + 4 * i + 2] = __fmaf_rn(__uint_as_float(v[4 * i + 2]) * f.z, pf, acc[c * 16 + 4 * i + 2] * alpha);
-            acc[c * 16 + 4 * i + 3] = __fmaf_rn(__uint_as_float(v[4 * i + 3]) * f.w, pf, acc[c * 16 + 4 * i + 3] * alpha);
+        for (int i = 0; i < 4; ++i) {
+          const float4 f = vf[c * 4 + i];
+          float2* a0 = reinterpret_cast<float2*>(&acc[c * 16 + 4 * i]);
+          float2* a1 = reinterpret_cast<float2*>(&acc[c * 16 + 4 * i + 2]);
+          const float2 t0 = __fmul2_rn(make_float2(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1])), make_float2(f.x, f.y));
+          const float2 t1 = __fmul2_rn(make_float2(__uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3])), make_float2(f.z, f.w));
+          if (keep) {
+            *a0 = __ffma2_rn(t0, pf2, *a0);
+            *a1 = __ffma2_rn(t1, pf2, *a1);
+          } else {
+            *a0 = __ffma2_rn(t0, pf2, __fmul2_rn(*a0, alpha2));
+            *a1 = __ffma2_rn(t1, pf2, __fmul2_rn(*a1, alpha2));
           }
         }
+      };
+      {
+        uint32_t va[16], vb[16];
+        const uint32_t t_src = lane_base + TM_T + c0;
+        tw::tmem_load_16_async(t_src, va);
+        tw::tmem_load_wait(va);
+        tw::tmem_load_16_async(t_src + 16, vb);
+        accumulate(va, 0);
+        tw::tmem_load_wait(vb);
+        tw::tmem_load_16_async(t_src + 32, va);
+        accumulate(vb, 1);
+        tw::tmem_load_wait(va);
+        tw::tmem_load_16_async(t_src + 48, vb);
+        accumulate(va, 2);
+        tw::tmem_load_wait(vb);
+        tw::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tw::mbar_arrive(tEmpty);
+        accumulate(vb, 3);
       }
-      tw::tc_fence_before();
       __syncwarp();
-      if (lane == 0) { tw::mbar_arrive(tEmpty); tw::mbar_arrive(vEmpty + s); }
+      if (lane == 0) tw::mbar_arrive(vEmpty + s);
     }
     if (ok && m < p.m) {
       const float inv = 1.f / den;
