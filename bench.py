@@ -236,8 +236,9 @@ METRIC_STEP = 'repaired NVFP4 GEMM effective TFLOPS on issued FP4 work (DiT deno
 
 
 def step_topology(world, cfg_parallel):
-    """(tp, cfg) for a world size: CFG branches split over GPU pairs from 4 GPUs on."""
-    cfg = cfg_parallel or (2 if world >= 4 else 1)
+    """(tp, cfg) for a world size: the two CFG branches are independent and split first (no collective inside the
+    step); tensor parallelism divides each branch from four GPUs on."""
+    cfg = cfg_parallel or (2 if world >= 2 else 1)
     return world // cfg, cfg
 
 
@@ -299,6 +300,7 @@ def measure_step(args, device, rank, world, dist):
     engine = StepEngine(run, plan=plan, topo=topo, branches=1)
     engine._branch_offset = topo.cfg_rank if cfg_par > 1 else 0
     model = dit.DiTModel(cfg, engine, topo, device)
+    model.row_sharded = not args.tp_allreduce
     batch = 2 // cfg_par
     g = torch.Generator().manual_seed(0)
     x_all = torch.randn(2, args.tokens, cfg.hidden, generator=g)
@@ -627,9 +629,10 @@ def main():
     ap.add_argument('--layers', default='qkv,out,ffn_up,ffn_down', help='subset of the projection set')
     ap.add_argument('--workload', default='auto', choices=('auto', 'projections', 'step', 'attention'))
     ap.add_argument('--model', default='nano', choices=('nano', 'super'))
+    ap.add_argument('--tp-allreduce', action='store_true', help='tensor-parallel step: all-reduce the row-split outputs instead of keeping the residual stream row-sharded')
     ap.add_argument('--blocks', type=int, default=0, help='override the number of DiT blocks (step workload)')
     ap.add_argument('--tokens', type=int, default=3840)
-    ap.add_argument('--cfg-parallel', type=int, default=0, help='CFG groups (0: 2 from four GPUs on, else 1)')
+    ap.add_argument('--cfg-parallel', type=int, default=0, help='CFG groups (0: 2 from two GPUs on, else 1; 1 forces tensor parallelism only)')
     ap.add_argument('--att-heads', type=int, default=32)
     args = ap.parse_args()
     if args.impl == 'reference':

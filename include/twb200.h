@@ -53,7 +53,8 @@ typedef struct TwQuantizeArgs {
   uint8_t* scales_swz;      /* optional out [planes, ceil(m/128)*128, k/16] atom layout */
   uint8_t* mask;            /* bool bytes [ceil(m/128), k/128]: in for repair == 2, out for repair == 3 */
   void* workspace;          /* tw_quantize_workspace(m, k) bytes of scratch */
-  int m, k, mp;             /* mp = ceil(m/16)*16 */
+  int m, k, mp;             /* mp: rows per plane of codes / scales, a multiple of 16 >= m (ceil(m/16)*16 when the planes
+                               hold this call's rows only; larger when they are a shard of a wider gathered tensor) */
   int repair;               /* 0 base plane only; 1 residual everywhere; 2 residual where mask is set,
                                zero codes and scales elsewhere; 3 residual everywhere and mask := the
                                top-`na` K128 blocks per M128 row block ranked by residual energy */
@@ -61,6 +62,7 @@ typedef struct TwQuantizeArgs {
   int factor_given;         /* nonzero: read *factor instead of reducing max|x| */
   float base, res, gain;    /* scale multipliers of the calibrated packer; 1,1,1 = plain */
   float energy;             /* < 1: energy-prefix stop of the selector; 1 = off */
+  int swz_rows;             /* rows per plane of scales_swz; 0 = ceil(m/128)*128, else a multiple of 128 not below that */
 } TwQuantizeArgs;
 size_t tw_quantize_workspace(int m, int k);
 int tw_quantize(const TwQuantizeArgs* args, void* stream);
@@ -101,7 +103,7 @@ typedef struct TwRepairIO {
   const int32_t *wi, *off, *wloc;              /* CSR over N128 blocks: k-block per slot, row offsets
                                                   [n/128+1], bank position per slot */
   const uint8_t* mask;                         /* bool [ceil(m/128), k/128], read at run time */
-  int32_t m, mp, n, k, na, hasw, cross, shared, dense, bank_blocks;
+  int32_t m, mp, n, k, na, hasw, cross, shared, dense, bank_blocks; /* mp: rows per plane of ac / as, a multiple of 16 >= m */
   /* extensions */
   const uint8_t* a1s_swz;  /* residual-plane activation scales, atom layout [ceil(m/128)*128, k/16] */
   const uint8_t* wrs_swz;  /* W1 bank scales, atom layout per tile: [slots][1024] */

@@ -130,6 +130,58 @@ def _run_plan(rank, world, port, results):
         dist.destroy_process_group()
 
 
+def _run_rows(rank, world, port, results):
+    """One batch entry under TP2 and a 2x plan: the row-sharded (reduce-scatter / all-gather of packed bytes) execution
+    gives the same bits as the all-reduce execution, for a token count that leaves padding rows in the last shard."""
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), NCCL_NVLS_ENABLE='0')
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
+    try:
+        from thunderworld_b200 import parallel
+        from thunderworld_b200.cosmos.budget import RepairPlan
+        from thunderworld_b200.cosmos.dit import DiTConfig, DiTModel
+        from thunderworld_b200.cosmos.engine import StepEngine
+        from thunderworld_b200.cosmos.settings import RunConfig
+        cfg = DiTConfig(hidden=512, heads=4, ffn=1024, blocks=2, seed=7)
+        h, f = cfg.hidden // 128, cfg.ffn // 128
+        lattice = {'qkv': (3 * h, h), 'out': (h, h), 'up': (f, h), 'down': (h, f)}
+        rng = np.random.default_rng(5)
+        linears = {}
+        for i in range(cfg.blocks):
+            for part, (nb, kb) in lattice.items():
+                row = {'a_blocks': kb // 2, 'w_blocks': sorted(int(t) for t in rng.permutation(nb * kb)[:nb * kb // 2]), 'cross': False}
+                for b in range(2):
+                    for ph in range(4):
+                        linears[f'{b}|{ph}|blocks.{i}.{part}'] = row
+        plan = RepairPlan(dict(schema_version=1, budget=2., steps=35, phases=[0, 7, 18, 28, 35], task='t2v',
+                               linears=linears, attention={}))
+        g = torch.Generator().manual_seed(0)
+        outs = {}
+        for tokens in (300, 512):                              # 300: the second shard holds 44 rows and 212 padding rows
+            x = torch.randn(1, tokens, cfg.hidden, generator=g).bfloat16().cuda()
+            mod = (torch.randn(1, cfg.blocks, 6, cfg.hidden, generator=g) * 0.1).bfloat16().cuda()
+            for name, sharded in (('rows', True), ('allreduce', False)):
+                topo = parallel.make_topology(tp_size=world)
+                engine = StepEngine(RunConfig(compute_budget=2.), plan=plan, topo=topo, branches=1)
+                model = DiTModel(cfg, engine, topo)
+                model.row_sharded = sharded
+                engine.warm_schedule(model, x=x, mod=mod)
+                a = engine(model, x=x, mod=mod)
+                b = engine(model, x=x, mod=mod)               # graph replay, collectives inside
+                assert torch.equal(a, b)
+                assert engine.device_status() == 0
+                outs[name] = a.clone()
+                engine.graphs.clear()
+                del model, engine
+                torch.cuda.synchronize()
+            assert outs['rows'].shape == (1, tokens, cfg.hidden)
+            assert torch.isfinite(outs['rows'].float()).all()
+            results[(rank, tokens)] = bool(torch.equal(outs['rows'], outs['allreduce']))
+    finally:
+        dist.destroy_process_group()
+
+
 def _launch(target, results):
     ctx = mp.get_context('spawn')
     with socket.socket() as s:
@@ -160,6 +212,13 @@ def test_tp2_row_split_under_a_2x_plan_matches_the_oracle_with_per_shard_masks()
     _launch(_run_plan, results)
     # each partial is within 1e-3 of its oracle; the sum of two bf16-rounded partials is rounded once more
     assert 'rel' in results and results['rel'] <= 2e-3, dict(results)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
+def test_tp2_row_sharded_step_equals_the_allreduce_step_bit_for_bit():
+    results = mp.get_context('spawn').Manager().dict()
+    _launch(_run_rows, results)
+    assert len(results) == 4 and all(results.values()), dict(results)
 
 
 def test_shard_factor_is_an_ieee_division_on_the_device():

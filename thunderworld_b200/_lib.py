@@ -20,7 +20,7 @@ class QuantizeArgs(ctypes.Structure):
     _fields_ = [(n, _vp) for n in ('x', 'prescale', 'sensitivity', 'factor', 'wg', 'alpha', 'codes', 'scales',
                                    'scales_swz', 'mask', 'workspace')] + \
                [(n, _i) for n in ('m', 'k', 'mp', 'repair', 'na', 'factor_given')] + \
-               [(n, _f) for n in ('base', 'res', 'gain', 'energy')]
+               [(n, _f) for n in ('base', 'res', 'gain', 'energy')] + [('swz_rows', _i)]
 
 
 class RepairIO(ctypes.Structure):

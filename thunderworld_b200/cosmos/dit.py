@@ -93,7 +93,11 @@ class DiTBlock(torch.nn.Module):
             tile_map = self._tile_map(nb, kb, split, tp, r, cfg.heads)
             controller.register_linear(name, split, tile_map, tp)
             self.split[part] = split
-            setattr(self, part, RepairLinear(_Source(w.contiguous()), controller, name, LinearSpec(), tile_map=tile_map))
+            # column-split shards rank A1 blocks with the column energy of the whole weight: the same support on
+            # every rank, and the one the unsharded layer selects
+            energy = full[part].float().square().sum(0) if split in ('column', 'qkv') and tp > 1 else None
+            setattr(self, part, RepairLinear(_Source(w.contiguous()), controller, name, LinearSpec(), tile_map=tile_map,
+                                             sensitivity=energy))
         del full, shards
 
     @staticmethod
@@ -132,6 +136,58 @@ class DiTBlock(torch.nn.Module):
             factor = parallel.global_factor_from_peak(stats[1:2].clone(), self.topo)
         return parallel.allreduce_sum(layer(x, factor=factor), self.topo)
 
+    def _gathered_input(self, layer, x_rows, stats, rows, tokens):
+        """Row-sharded producer -> column-split layer: global factor from the shards' maxima, local quantization,
+        all-gather of the packed bytes. Returns the Packed activation of all tokens."""
+        layer.prepare(tokens)
+        factor = parallel.global_factor_from_peak(stats[1:2].clone(), self.topo)
+        return layer.pack_shard(x_rows, factor, rows, tokens, self.topo)
+
+    def _row_split_scatter(self, layer, x, rows_padded, stats=None):
+        """Row-split linear whose partial sums are reduce-scattered over token rows: returns this rank's summed rows
+        [rows_padded / tp, hidden]."""
+        if stats is None:
+            factor = parallel.global_factor(x, self.topo)
+        else:
+            factor = parallel.global_factor_from_peak(stats[1:2].clone(), self.topo)
+        y = layer(x, factor=factor)                              # [tokens, hidden] partial sums
+        if rows_padded != y.shape[0]:
+            padded = torch.zeros((rows_padded, y.shape[1]), device=y.device, dtype=y.dtype)
+            padded[:y.shape[0]] = y
+            y = padded
+        return parallel.reduce_scatter_rows(y, self.topo)
+
+    def forward_rows(self, x_rows, mod, tokens):
+        """Sequence-parallel form of forward() for one batch entry under tensor parallelism: `x_rows`
+        [rows, hidden] is this rank's share of the residual stream (rows = padded tokens / tp, whole M128 blocks;
+        rows past the end of the sequence are padding), updated in place. Pointwise producers and the quantizer run
+        on the shard; packed bytes are all-gathered in front of the column-split layers and the partial sums of the
+        row-split layers are reduce-scattered. Same bits as forward() on the all-reduce path."""
+        rows, h = x_rows.shape
+        _, first, valid = parallel.shard_rows_of(tokens, self.topo)
+        rows_padded = rows * self.topo.tp_size
+        shift1, scale1, gate1, shift2, scale2, gate2 = mod.unbind(0)
+        live = x_rows[:valid].unsqueeze(0)                       # [1, valid, hidden] view: padding rows never enter a maximum
+        y, stats = ops.rms_norm(live, shift=shift1, scale=scale1, want_factor=True, return_stats=True)
+        packed = self._gathered_input(self.qkv, y[0], stats, rows, tokens)
+        qkv = self.qkv.run_rows(tokens, packed).reshape(1, tokens, 3, self.local_heads, 128)
+        q, k, v = qkv.unbind(2)
+        if self.cfg.rope:
+            cos, sin = self.controller_tables(tokens, x_rows.device)
+            q = ops.rope_heads(q, cos, sin, norm=self.cfg.qk_norm)
+            k = ops.rope_heads(k, cos, sin, norm=self.cfg.qk_norm)
+        elif self.cfg.qk_norm:
+            q, k = ops.rms_norm_heads(q), ops.rms_norm_heads(k)
+        a = self.controller.attend(self.index, q, k, v).reshape(tokens, self.local_heads * 128)
+        part = self._row_split_scatter(self.out, a, rows_padded)
+        ops.gate_residual_(x_rows.unsqueeze(0), gate1, part.unsqueeze(0))
+        y, stats = ops.rms_norm(live, shift=shift2, scale=scale2, want_factor=True, return_stats=True)
+        packed = self._gathered_input(self.up, y[0], stats, rows, tokens)
+        u, ustats = self.up.run_rows(tokens, packed, activation='gelu_tanh')
+        part = self._row_split_scatter(self.down, u, rows_padded, ustats)
+        ops.gate_residual_(x_rows.unsqueeze(0), gate2, part.unsqueeze(0))
+        return x_rows
+
     def forward(self, x, mod):
         """x bf16 [batch, tokens, hidden], updated in place; mod [6, batch, hidden] contiguous."""
         b, s, h = x.shape
@@ -159,12 +215,26 @@ class DiTModel(torch.nn.Module):
         super().__init__()
         self.cfg = cfg
         self.topo = topo or parallel.Topology()
+        self.row_sharded = True       # tensor-parallel runs of one batch entry keep the residual stream row-sharded
         self.blocks = torch.nn.ModuleList(DiTBlock(cfg, i, controller, self.topo, device) for i in range(cfg.blocks))
 
     def forward(self, x, mod):
         """x bf16 [batch, tokens, hidden]; mod bf16 [batch, blocks, 6, hidden] (AdaLN shift/scale/gate)."""
-        x = x.clone()                                         # blocks update the residual stream in place
         mods = mod.permute(1, 2, 0, 3).contiguous()           # [blocks, 6, batch, hidden]
+        topo = self.topo
+        if topo.tp_size > 1 and x.shape[0] == 1 and self.row_sharded:
+            # the residual stream lives row-sharded between the projections (see DiTBlock.forward_rows)
+            tokens, hidden = x.shape[1], x.shape[2]
+            rows, first, valid = parallel.shard_rows_of(tokens, topo)
+            mine = torch.zeros((rows, hidden), device=x.device, dtype=x.dtype)
+            mine[:valid] = x[0, first:first + valid]
+            for i, block in enumerate(self.blocks):
+                block.forward_rows(mine, mods[i], tokens)
+            mine = ops.rms_norm(mine.unsqueeze(0))[0]
+            full = torch.empty((rows * topo.tp_size, hidden), device=x.device, dtype=x.dtype)
+            parallel.all_gather_rows([(full, mine)], topo)
+            return full[:tokens].unsqueeze(0)
+        x = x.clone()                                         # blocks update the residual stream in place
         for i, block in enumerate(self.blocks):
             x = block(x, mods[i])
         return ops.rms_norm(x)

@@ -18,8 +18,10 @@ from .assets import compact, expand
 
 
 class RepairLinear(torch.nn.Module):
-    def __init__(self, source, controller, name, spec, asset=None, tile_map=None):
+    def __init__(self, source, controller, name, spec, asset=None, tile_map=None, sensitivity=None):
         super().__init__()
+        # sensitivity: selector weights [K] to use instead of the column energy of `source` (a column-split shard
+        # passes the energy of the whole weight, so that every rank selects what the unsharded layer selects)
         # tile_map: plan tile ids of the full layer -> ids of this (tensor-parallel) shard's lattice
         self.tile_map = tile_map
         self.in_features, self.out_features = source.in_features, source.out_features
@@ -37,7 +39,8 @@ class RepairLinear(torch.nn.Module):
             asset = dict(codes=codes.cpu(), scales=scales.cpu(), factor=factor.cpu(), prescale=torch.ones(k),
                          identity_prescale=True, score=score.cpu(), bias=None if source.bias is None else source.bias.detach().cpu())
             if plan is not None:
-                asset.update(selector='residual_sensitivity', activation_sensitivity=w.float().square().sum(0).cpu())
+                asset.update(selector='residual_sensitivity', activation_sensitivity=(
+                    w.float().square().sum(0) if sensitivity is None else sensitivity.float()).cpu())
         # with a plan only the union of W1 tiles any phase/branch selects is kept
         self.weight_union = None
         if plan is not None:
@@ -114,43 +117,96 @@ class RepairLinear(torch.nn.Module):
         self.ops[key] = op
         self.bound = op
 
-    def _compute(self, x, factor=None, packed=None, activation=None):
+    def _pack(self, x, factor=None, mask=None, out=None):
+        """Quantize x [rows, k] for the bound operator. The A1 support of a partial repair is written into `mask`
+        (default: the operator's own [ceil(rows/128), k/128]); `out`: preallocated planes (ops.Packed)."""
         op = self.bound
         m, k = x.shape
         kb = k // 128
+        mask = op.am if mask is None else mask
         base, res = self.asset.get('activation_scale', (1., 1.))
         identity = bool(self.asset.get('identity_prescale', False))
+        common = dict(wg=op.wg, base=base, res=res, out=out)
+        d = None if identity else op.d               # an identity prescale is bf16(x * 1) = x: skip the multiply
+        if self.asset.get('selector') == 'residual_sensitivity' and 0 < op.na < kb:
+            # online current-residual selection: mask written in place, then read by the GEMM
+            return ops.quantize(x, d, repair=3, na=op.na, sensitivity=self.sensitivity, mask=mask,
+                                factor=factor if identity else None, energy=self.repair_energy, **common)
+        if 0 < op.na < kb:                           # sampled-energy selector of assets without sensitivities
+            mask.copy_(sampled_block_rank(x, op.d, m, k) < op.na)
+        mode = 0 if op.na == 0 else (1 if op.na == kb else 2)
+        use_factor = factor if (base, res) == (1., 1.) else None
+        return ops.quantize(x, d, repair=mode, mask=mask if mode == 2 else None, factor=use_factor, **common)
+
+    def _compute(self, x, factor=None, packed=None, activation=None):
         if packed is None:
-            common = dict(wg=op.wg, base=base, res=res)
-            d = None if identity else op.d               # an identity prescale is bf16(x * 1) = x: skip the multiply
-            if self.asset.get('selector') == 'residual_sensitivity' and 0 < op.na < kb:
-                # online current-residual selection: mask written in place, then read by the GEMM
-                packed = ops.quantize(x, d, repair=3, na=op.na, sensitivity=self.sensitivity, mask=op.am,
-                                      factor=factor if identity else None, energy=self.repair_energy, **common)
-            else:
-                if 0 < op.na < kb:                       # sampled-energy selector of assets without sensitivities
-                    op.am.copy_(sampled_block_rank(x, op.d, m, k) < op.na)
-                mode = 0 if op.na == 0 else (1 if op.na == kb else 2)
-                use_factor = factor if (base, res) == (1., 1.) else None
-                packed = ops.quantize(x, d, repair=mode, mask=op.am if mode == 2 else None, factor=use_factor, **common)
+            packed = self._pack(x, factor)
         # the bias is added in fp32 before the single bf16 rounding of the epilogue (TwRepairIO.bias)
-        return op.run_packed(x, packed, bias=self.bias, activation=activation, want_stats=activation is not None)
+        return self.bound.run_packed(x, packed, bias=self.bias, activation=activation, want_stats=activation is not None)
+
+    def pack_shard(self, x_rows, factor, rows, total_rows, topo):
+        """Row-sharded input of a column-split layer: quantize this rank's `x_rows` [valid, k] (valid <= rows, the
+        shard's padded height, a multiple of 128) with the tensor-wide `factor`, then all-gather the packed planes,
+        the atom-layout scales and the A1 support of every shard. Returns the Packed of all `total_rows` rows; the
+        operator's own support (`bound.am`) is overwritten with the gathered one. Called after `prepare`."""
+        op = self.bound
+        k = self.in_features
+        kb = k // 128
+        if not self.asset.get('identity_prescale', False) or self.asset.get('activation_scale', (1., 1.)) != (1., 1.):
+            raise ValueError('row-sharded packing needs the tensor factor from the producer: identity prescale only')
+        dev = self.sensitivity.device
+        planes = 1 if op.na == 0 else 2
+        tp = topo.tp_size
+        local = ops.Packed(torch.empty((planes, rows, k // 2), device=dev, dtype=torch.uint8),
+                           torch.empty((planes, rows, k // 16), device=dev, dtype=torch.float8_e4m3fn), factor, rows,
+                           torch.empty((planes, rows, k // 16), device=dev, dtype=torch.uint8),
+                           torch.empty((), device=dev, dtype=torch.float32), None)
+        partial = 0 < op.na < kb
+        local_mask = torch.zeros((rows // 128, kb), device=dev, dtype=torch.bool) if partial else None
+        valid = x_rows.shape[0]
+        if valid:
+            self._pack(x_rows, factor, mask=None if local_mask is None else local_mask[:ops.cdiv(valid, 128)], out=local)
+        full = ops.Packed(torch.empty((planes, rows * tp, k // 2), device=dev, dtype=torch.uint8),
+                          torch.empty((planes, rows * tp, k // 16), device=dev, dtype=torch.float8_e4m3fn), factor, rows * tp,
+                          torch.empty((planes, rows * tp, k // 16), device=dev, dtype=torch.uint8), local.alpha, None)
+        pieces = []
+        for plane in range(planes):
+            pieces += [(full.codes[plane], local.codes[plane]), (full.scales[plane], local.scales[plane]),
+                       (full.scales_swz[plane], local.scales_swz[plane])]
+        if partial:
+            gathered = torch.empty((rows * tp // 128, kb), device=dev, dtype=torch.bool)
+            pieces.append((gathered, local_mask))
+        from .. import parallel
+        parallel.all_gather_rows(pieces, topo)
+        if partial:
+            op.am.copy_(gathered[:op.am.shape[0]])
+        return full
+
+    def prepare(self, rows):
+        """Controller bookkeeping of forward() for `rows` input rows without running anything: binds (while warming:
+        builds and records) the operator of the current repair spec."""
+        c = self.controller
+        spec = c.linear_spec(self.name, self.default)
+        key = (rows, spec.key)
+        if c.warming:
+            self.prepare_shape(rows, spec)
+            c.record_linear(self.name, (rows, self.in_features), self.out_features, spec, self.bound)
+        elif key not in self.ops:
+            raise RuntimeError(f'Unwarmed projection {self.name}: {key}')
+        else:
+            self.bound = self.ops[key]
+
+    def run_rows(self, rows, packed, activation=None):
+        """GEMM of the bound operator on `rows` rows of an already packed (gathered) activation."""
+        shape_only = torch.empty((rows, 0), device=packed.codes.device, dtype=torch.bfloat16)
+        return self.bound.run_packed(shape_only, packed, bias=self.bias, activation=activation, want_stats=activation is not None)
 
     def forward(self, x, *, factor=None, packed=None, activation=None):
         """activation='gelu_tanh': the activation is applied in the GEMM epilogue and the call returns
         (y, stats) with stats = (max|y| / 2688, max|y|), as ops.activate_with_factor(..., return_stats=True) would."""
         shape = x.shape
         flat = x.reshape(-1, self.in_features).contiguous()
-        c = self.controller
-        spec = c.linear_spec(self.name, self.default)
-        key = (len(flat), spec.key)
-        if c.warming:
-            self.prepare_shape(len(flat), spec)
-            c.record_linear(self.name, flat.shape, self.out_features, spec, self.bound)
-        elif key not in self.ops:
-            raise RuntimeError(f'Unwarmed projection {self.name}: {key}')
-        else:
-            self.bound = self.ops[key]
+        self.prepare(len(flat))
         if activation is not None:
             y, stats = self._compute(flat, factor, packed, activation)
             return y.reshape(*shape[:-1], self.out_features), stats

@@ -6,7 +6,7 @@ extern "C" const char* tw_status(int status) {
   switch (status) {
     case TW_OK: return "success";
     case TW_ERR_ARGUMENT: return "invalid argument (null pointer, non-positive size or inconsistent flags)";
-    case TW_ERR_SHAPE: return "unsupported shape (n and k must be multiples of 128, mp = ceil(m/16)*16)";
+    case TW_ERR_SHAPE: return "unsupported shape (n and k must be multiples of 128, mp a multiple of 16 not below m)";
     case TW_ERR_ALIGNMENT: return "pointer is not 16-byte aligned";
     case TW_ERR_MISSING_SWIZZLED: return "a repair term was requested without its atom-layout scales";
     case TW_ERR_TENSOR_MAP: return "cuTensorMapEncodeTiled rejected a tensor map";

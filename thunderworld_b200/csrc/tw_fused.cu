@@ -643,7 +643,7 @@ extern "C" int tw_fused(int m, int n, int k, const void* a_codes, const void* w_
   if (m <= 0 || n <= 0 || k <= 0) return TW_ERR_ARGUMENT;
   if (n % 128 || k % 128) return TW_ERR_SHAPE;
   if (k / 128 > KB_MAX) return TW_ERR_TOO_LARGE;
-  if (io->m != m || io->n != n || io->k != k || io->mp != (m + 15) / 16 * 16) return TW_ERR_SHAPE;
+  if (io->m != m || io->n != n || io->k != k || io->mp < (m + 15) / 16 * 16 || io->mp % 16) return TW_ERR_SHAPE;
   if (io->na < 0 || io->na > k / 128) return TW_ERR_ARGUMENT;
   if (io->na > 0 && !io->a1s_swz) return TW_ERR_MISSING_SWIZZLED;
   if (io->na > 0 && (io->mask_per_n || io->na < k / 128) && !io->mask) return TW_ERR_ARGUMENT;

@@ -24,6 +24,7 @@ struct PackParams {
   uint8_t* codes;
   uint8_t* scales;
   uint8_t* scales_swz;
+  int swz_rows;             // rows per plane of scales_swz
   const uint8_t* mask;
   const unsigned* amax_bits;
   float* scores;
@@ -252,7 +253,7 @@ __device__ __forceinline__ void pack_tile(const PackParams& p, int kb, int mbi, 
     if (p.scales_swz && (cg & 3) == 0) {
       uint32_t off = scale_offset(row, kb * 8 + cg, cols16);
       *reinterpret_cast<uint32_t*>(p.scales_swz + off) = lo0;
-      if (planes2) *reinterpret_cast<uint32_t*>(p.scales_swz + (size_t)p.mb * 128 * cols16 + off) = lo1;
+      if (planes2) *reinterpret_cast<uint32_t*>(p.scales_swz + (size_t)p.swz_rows * cols16 + off) = lo1;
     }
   }
   };
@@ -474,7 +475,8 @@ extern "C" size_t tw_quantize_workspace(int m, int k) {
 extern "C" int tw_quantize(const TwQuantizeArgs* a, void* stream_) {
   if (!a || !a->x || !a->codes || !a->scales || !a->factor || !a->workspace) return TW_ERR_ARGUMENT;
   if (a->m <= 0 || a->k <= 0) return TW_ERR_ARGUMENT;
-  if (a->k % 128 || a->mp != (a->m + 15) / 16 * 16) return TW_ERR_SHAPE;
+  if (a->k % 128 || a->mp < (a->m + 15) / 16 * 16 || a->mp % 16) return TW_ERR_SHAPE;
+  if (a->swz_rows && (a->swz_rows % 128 || a->swz_rows < (a->m + 127) / 128 * 128)) return TW_ERR_SHAPE;
   if (a->repair < 0 || a->repair > 3) return TW_ERR_ARGUMENT;
   if ((a->repair == 2 || a->repair == 3) && !a->mask) return TW_ERR_ARGUMENT;
   if (a->repair == 3 && (!a->sensitivity || a->na <= 0 || a->na >= a->k / 128)) return TW_ERR_ARGUMENT;
@@ -493,6 +495,7 @@ extern "C" int tw_quantize(const TwQuantizeArgs* a, void* stream_) {
   p.codes = a->codes; p.scales = a->scales; p.scales_swz = a->scales_swz; p.mask = a->mask;
   p.amax_bits = amax; p.scores = scores;
   p.m = a->m; p.k = a->k; p.mp = a->mp; p.mb = mb;
+  p.swz_rows = a->swz_rows ? a->swz_rows : mb * 128;
   p.repair = a->repair; p.factor_given = a->factor_given;
   p.base = a->base; p.res = a->res; p.gain = a->gain;
   int dev = 0, sms = 0, coop = 0;

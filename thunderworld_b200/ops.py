@@ -80,8 +80,11 @@ def quantize(x, prescale=None, *, repair=1, mask=None, na=0, sensitivity=None, f
     if k % 128:
         raise ValueError('K must be a multiple of 128')
     lib = _lib.load()
-    mp = cdiv(m, 16) * 16
+    # with preallocated outputs the planes may hold more rows than m (a shard of a larger gathered tensor)
+    mp = cdiv(m, 16) * 16 if out is None else int(out.codes.shape[1])
     mb = cdiv(m, 128)
+    if mp < cdiv(m, 16) * 16:
+        raise ValueError('preallocated planes are too small')
     planes = 2 if repair else 1
     dev = x.device
     if out is None:
@@ -103,7 +106,7 @@ def quantize(x, prescale=None, *, repair=1, mask=None, na=0, sensitivity=None, f
     args = _lib.QuantizeArgs(_ptr(x), _ptr(prescale), _ptr(sensitivity), _ptr(fac), _ptr(wg), _ptr(alpha),
                              _ptr(codes), _ptr(scales), _ptr(swz), _ptr(mask), _ptr(workspace),
                              m, k, mp, int(repair), int(na), int(factor is not None),
-                             float(base), float(res), float(gain), float(energy))
+                             float(base), float(res), float(gain), float(energy), int(swz.shape[1]))
     with torch.cuda.device(dev):
         _lib.check(lib.tw_quantize(ctypes.byref(args), _stream(dev)))
     return Packed(codes, scales, fac, mp, swz, alpha, mask)
@@ -248,9 +251,9 @@ def activate_with_factor(a, b=None, *, mode=None, want_factor=True, return_stats
     return y, (None if stats is None else (stats if return_stats else stats[0]))
 
 
-def rms_norm(x, weight=None, eps=1e-6, *, shift=None, scale=None, want_factor=False):
+def rms_norm(x, weight=None, eps=1e-6, *, shift=None, scale=None, want_factor=False, return_stats=False):
     """RMSNorm over the last dimension, optional weight, optional AdaLN modulation with shift/scale of shape
-    [batch, hidden] (x is [batch, tokens, hidden]). Returns y or (y, factor)."""
+    [batch, hidden] (x is [batch, tokens, hidden]). Returns y or (y, factor); return_stats: (y, (factor, max|y|))."""
     if torch.is_grad_enabled() and x.requires_grad:
         raise RuntimeError('Fused RMSNorm requires inference mode')
     _check_bf16(x, weight, shift, scale)
@@ -270,7 +273,9 @@ def rms_norm(x, weight=None, eps=1e-6, *, shift=None, scale=None, want_factor=Fa
     stats, scratch = _stats(x.device, want_factor)
     _lib.check(_lib.load().tw_rms_norm(_ptr(x), _ptr(weight), _ptr(shift), _ptr(scale), _ptr(y), _ptr(stats), _ptr(scratch),
                                        rows, hidden, per_batch, float(eps), _stream(x.device)))
-    return (y, stats[0]) if want_factor else y
+    if not want_factor:
+        return y
+    return (y, stats) if return_stats else (y, stats[0])
 
 
 def rms_norm_heads(x, eps=1e-6):

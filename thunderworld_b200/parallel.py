@@ -8,7 +8,12 @@ tools/contribution_study/super_runtime.py:74-102); this module is what the shard
 * row split (out-proj, FFN-down): K128 blocks are divided; the tensor-wide activation factor must be the
   global one, so ranks exchange max|x| (4 bytes, MAX) before quantizing, and partial outputs are summed;
 * W1 tile ids `nb*KB + kb` of a plan are remapped to the shard's own lattice;
-* CFG split: ranks are arranged as [cfg][tp]; each CFG group runs one of the cond / uncond branches.
+* CFG split: ranks are arranged as [cfg][tp]; each CFG group runs one of the cond / uncond branches;
+* row sharding of the residual stream between the projections (sequence parallelism): the partial sums of a
+  row-split layer are reduce-scattered over token rows instead of all-reduced, every rank runs the pointwise
+  producers and the quantizer on its rows only, and the packed bytes (0.56 B per element instead of 2) are
+  all-gathered for the next column-split layer. Shards are whole M128 row blocks, so block-wise selection and
+  the atom-layout scales of a shard are exactly the corresponding part of the unsharded result.
 """
 from dataclasses import dataclass
 import torch
@@ -156,3 +161,50 @@ def guide(branch_output, scale, topo):
     both = [torch.empty_like(branch_output) for _ in range(2)]
     dist.all_gather(both, branch_output.contiguous(), group=topo.cfg_group)
     return both[1] + scale * (both[0] - both[1])
+
+
+# ---- row sharding of the residual stream (sequence parallelism) -----------------------------------------------
+def padded_rows(m, tp):
+    """Rows of the token dimension rounded up so that every shard is a whole number of M128 blocks."""
+    step = 128 * tp
+    return -(-m // step) * step
+
+
+def shard_rows_of(m, topo):
+    """(rows per shard, first row, valid rows) of this rank's share of m token rows."""
+    per = padded_rows(m, topo.tp_size) // topo.tp_size
+    first = topo.tp_rank * per
+    return per, first, max(0, min(per, m - first))
+
+
+def _backend(group):
+    return dist.get_backend(group) if dist.is_initialized() else None
+
+
+def reduce_scatter_rows(partial, topo):
+    """partial [padded rows, hidden] (this rank's partial sums, padding rows zero) -> this rank's summed rows
+    [padded rows / tp, hidden]."""
+    per = partial.shape[0] // topo.tp_size
+    if _backend(topo.tp_group) == 'nccl':
+        out = torch.empty((per, partial.shape[1]), device=partial.device, dtype=partial.dtype)
+        dist.reduce_scatter_tensor(out, partial, op=dist.ReduceOp.SUM, group=topo.tp_group)
+        return out
+    total = partial.clone()                                   # backends without reduce-scatter (CPU tests)
+    dist.all_reduce(total, op=dist.ReduceOp.SUM, group=topo.tp_group)
+    return total[topo.tp_rank * per:(topo.tp_rank + 1) * per].contiguous()
+
+
+def all_gather_rows(pieces, topo):
+    """pieces: list of (full, local) tensor pairs; full = concatenation of every rank's `local` along dim 0.
+    On NCCL all pieces travel in one grouped launch."""
+    bytes_of = lambda t: t.view(torch.uint8) if t.dtype in (torch.bool, torch.float8_e4m3fn) else t
+    pairs = [(bytes_of(f), bytes_of(l.contiguous())) for f, l in pieces]
+    if _backend(topo.tp_group) == 'nccl':
+        with dist._coalescing_manager(group=topo.tp_group, device=pairs[0][0].device, async_ops=False):
+            for full, local in pairs:
+                dist.all_gather_into_tensor(full, local, group=topo.tp_group)
+    else:
+        for full, local in pairs:
+            parts = [torch.empty_like(local) for _ in range(topo.tp_size)]
+            dist.all_gather(parts, local, group=topo.tp_group)
+            full.copy_(torch.cat(parts, 0))
