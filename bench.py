@@ -300,7 +300,7 @@ def measure_step(args, device, rank, world, dist):
     engine = StepEngine(run, plan=plan, topo=topo, branches=1)
     engine._branch_offset = topo.cfg_rank if cfg_par > 1 else 0
     model = dit.DiTModel(cfg, engine, topo, device)
-    model.row_sharded = not args.tp_allreduce
+    model.row_sharded = args.tp_row_sharded
     batch = 2 // cfg_par
     g = torch.Generator().manual_seed(0)
     x_all = torch.randn(2, args.tokens, cfg.hidden, generator=g)
@@ -629,7 +629,7 @@ def main():
     ap.add_argument('--layers', default='qkv,out,ffn_up,ffn_down', help='subset of the projection set')
     ap.add_argument('--workload', default='auto', choices=('auto', 'projections', 'step', 'attention'))
     ap.add_argument('--model', default='nano', choices=('nano', 'super'))
-    ap.add_argument('--tp-allreduce', action='store_true', help='tensor-parallel step: all-reduce the row-split outputs instead of keeping the residual stream row-sharded')
+    ap.add_argument('--tp-row-sharded', action='store_true', help='tensor-parallel step: keep the residual stream row-sharded (reduce-scatter / all-gather of packed bytes) instead of all-reducing the row-split outputs')
     ap.add_argument('--blocks', type=int, default=0, help='override the number of DiT blocks (step workload)')
     ap.add_argument('--tokens', type=int, default=3840)
     ap.add_argument('--cfg-parallel', type=int, default=0, help='CFG groups (0: 2 from two GPUs on, else 1; 1 forces tensor parallelism only)')

@@ -215,7 +215,9 @@ class DiTModel(torch.nn.Module):
         super().__init__()
         self.cfg = cfg
         self.topo = topo or parallel.Topology()
-        self.row_sharded = True       # tensor-parallel runs of one batch entry keep the residual stream row-sharded
+        # tensor-parallel runs of one batch entry may keep the residual stream row-sharded (forward_rows); off by
+        # default: with two shards the extra collectives cost more than the halved pointwise work saves
+        self.row_sharded = False
         self.blocks = torch.nn.ModuleList(DiTBlock(cfg, i, controller, self.topo, device) for i in range(cfg.blocks))
 
     def forward(self, x, mod):

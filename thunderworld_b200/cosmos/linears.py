@@ -138,11 +138,11 @@ class RepairLinear(torch.nn.Module):
         use_factor = factor if (base, res) == (1., 1.) else None
         return ops.quantize(x, d, repair=mode, mask=mask if mode == 2 else None, factor=use_factor, **common)
 
-    def _compute(self, x, factor=None, packed=None, activation=None):
+    def _compute(self, x, factor=None, packed=None, activation=None, out=None):
         if packed is None:
             packed = self._pack(x, factor)
         # the bias is added in fp32 before the single bf16 rounding of the epilogue (TwRepairIO.bias)
-        return self.bound.run_packed(x, packed, bias=self.bias, activation=activation, want_stats=activation is not None)
+        return self.bound.run_packed(x, packed, out=out, bias=self.bias, activation=activation, want_stats=activation is not None)
 
     def pack_shard(self, x_rows, factor, rows, total_rows, topo):
         """Row-sharded input of a column-split layer: quantize this rank's `x_rows` [valid, k] (valid <= rows, the
@@ -201,7 +201,7 @@ class RepairLinear(torch.nn.Module):
         shape_only = torch.empty((rows, 0), device=packed.codes.device, dtype=torch.bfloat16)
         return self.bound.run_packed(shape_only, packed, bias=self.bias, activation=activation, want_stats=activation is not None)
 
-    def forward(self, x, *, factor=None, packed=None, activation=None):
+    def forward(self, x, *, factor=None, packed=None, activation=None, out=None):
         """activation='gelu_tanh': the activation is applied in the GEMM epilogue and the call returns
         (y, stats) with stats = (max|y| / 2688, max|y|), as ops.activate_with_factor(..., return_stats=True) would."""
         shape = x.shape
@@ -210,4 +210,4 @@ class RepairLinear(torch.nn.Module):
         if activation is not None:
             y, stats = self._compute(flat, factor, packed, activation)
             return y.reshape(*shape[:-1], self.out_features), stats
-        return self._compute(flat, factor, packed).reshape(*shape[:-1], self.out_features)
+        return self._compute(flat, factor, packed, out=out).reshape(*shape[:-1], self.out_features)
