@@ -84,13 +84,45 @@ def _cfg_worker(rank, world, port, results):
         dist.destroy_process_group()
 
 
+def _rows_worker(rank, world, port, results):
+    """Row sharding of the residual stream: shard geometry with padding rows, reduce-scatter of partial sums over
+    token rows, all-gather of several per-shard pieces (bytes, bool support) into row order."""
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    try:
+        topo = parallel.make_topology(tp_size=2, cfg_size=1)
+        assert parallel.padded_rows(300, 2) == 512 and parallel.padded_rows(512, 2) == 512 and parallel.padded_rows(3840, 4) == 4096
+        rows, first, valid = parallel.shard_rows_of(300, topo)
+        assert (rows, first, valid) == ((256, 0, 256) if rank == 0 else (256, 256, 44))
+        g = torch.Generator().manual_seed(1)
+        parts = [torch.randn(512, 8, generator=g) for _ in range(2)]     # both ranks draw both partial sums
+        mine = parallel.reduce_scatter_rows(parts[rank].clone(), topo)
+        assert mine.shape == (256, 8)
+        assert torch.allclose(mine, (parts[0] + parts[1])[rank * 256:(rank + 1) * 256])
+        codes = torch.full((256, 4), rank + 1, dtype=torch.uint8)
+        support = torch.zeros((2, 3), dtype=torch.bool)
+        support[rank, rank] = True
+        full_codes = torch.empty((512, 4), dtype=torch.uint8)
+        full_support = torch.empty((4, 3), dtype=torch.bool)
+        parallel.all_gather_rows([(full_codes, codes), (full_support, support)], topo)
+        assert torch.equal(full_codes[:256], torch.full((256, 4), 1, dtype=torch.uint8))
+        assert torch.equal(full_codes[256:], torch.full((256, 4), 2, dtype=torch.uint8))
+        want = torch.zeros((4, 3), dtype=torch.bool)
+        want[0, 0] = True
+        want[3, 1] = True
+        assert torch.equal(full_support, want)
+        results[rank] = 1
+    finally:
+        dist.destroy_process_group()
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(('127.0.0.1', 0))
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize('worker', [_worker, _cfg_worker])
+@pytest.mark.parametrize('worker', [_worker, _cfg_worker, _rows_worker])
 def test_two_rank_gloo(worker):
     ctx = mp.get_context('spawn')
     results = ctx.Manager().dict()
