@@ -3,7 +3,7 @@ with E4M3 block scales in the 128x4 atom layout) at 8192^3, as a burst (best of 
 back for ~3 s, median SM clock sampled with nvidia-smi). This is the measured denominator beside the nominal
 9 PFLOP/s figure; it is a baseline script, not part of the product path.
 
-    python baseline/fp4_peak_probe.py [--size 8192] [--out gpurun_out/fp4_peak.json]
+    python baseline/fp4_peak_probe.py [--size 8192] [--out FILE.json]
 """
 import argparse
 import json

@@ -5,7 +5,7 @@ issued-work plans. Both kernels get byte-identical packed operands (this reposit
 selector's realised mask, the same W1 bank) through the same C ABI; only the scale-layout pointers differ
 (the reference reads row-major residual scales, tw_fused reads atom-layout ones).
 
-    python baseline/reference_sm100.py [--steps 20] [--out gpurun_out/reference_sm100.json]
+    python baseline/reference_sm100.py [--steps 20] [--out FILE.json]
 
 Protocol: every (layer, kernel) launch is captured in its own CUDA Graph; per round all launches are queued
 behind a spin kernel and bracketed by CUDA events; the layers rotate so consecutive launches of one kernel
