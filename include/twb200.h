@@ -200,7 +200,7 @@ int tw_rms_norm_heads(const void* x, void* y, long long tokens, int heads, long 
                       float eps, void* stream);
 /* Rotary embedding of 128-wide head rows of a strided bf16 view [tokens, heads, 128], with the reference's rounding
  * sequence (thunderworld_fp4/cosmos/pipeline_tuning.py:42-63, fused_rope): y[d] = bf16(bf16(x[d] cos[d]) + bf16(rot[d]
- * sin[d])), rot[d] = -x[d + 64] (d < 64) or x[d - 64]. cos / sin tables are [table_rows, 128], float32 or bf16; row
+ * sin[d])), rot[d] = -x[d + 64] (d < 64) or x[d - 64]. cos / sin tables are [table_rows, 128], float32 or bf16, 16-byte aligned; row
  * token % table_rows applies to a token. norm != 0: the head RMSNorm of tw_rms_norm_heads runs first in the same pass
  * (its bf16 result is what gets rotated, as when the two kernels run one after the other). */
 int tw_rope_heads(const void* x, void* y, long long tokens, int heads, long long stride_token, long long stride_head,

@@ -198,15 +198,38 @@ __global__ void __launch_bounds__(256) head_rows_kernel(const __nv_bfloat16* __r
     for (int i = 0; i < 16; ++i) v[i] = ROPE ? __bfloat162float(__float2bfloat16_rn(v[i] * rstd)) : v[i] * rstd;
   }
   if (ROPE) {
+    // the 16 table entries of this lane, fetched as 16-byte vectors (the tables are rows of 128 entries, so a
+    // lane's slice is 16-byte aligned for both table types)
     const long long t = (token % table_rows) * 128 + lane8 * 16;
+    float c[16], sn[16];
+    if (live) {
+      if (sizeof(TableT) == 4) {
+        const float4* c4 = reinterpret_cast<const float4*>(cos_t + t);
+        const float4* s4 = reinterpret_cast<const float4*>(sin_t + t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float4 a = __ldg(c4 + i), b = __ldg(s4 + i);
+          c[4 * i] = a.x; c[4 * i + 1] = a.y; c[4 * i + 2] = a.z; c[4 * i + 3] = a.w;
+          sn[4 * i] = b.x; sn[4 * i + 1] = b.y; sn[4 * i + 2] = b.z; sn[4 * i + 3] = b.w;
+        }
+      } else {
+        const uint4* c4 = reinterpret_cast<const uint4*>(cos_t + t);
+        const uint4* s4 = reinterpret_cast<const uint4*>(sin_t + t);
+        unpack8(__ldg(c4), *reinterpret_cast<float(*)[8]>(&c[0]));
+        unpack8(__ldg(c4 + 1), *reinterpret_cast<float(*)[8]>(&c[8]));
+        unpack8(__ldg(s4), *reinterpret_cast<float(*)[8]>(&sn[0]));
+        unpack8(__ldg(s4 + 1), *reinterpret_cast<float(*)[8]>(&sn[8]));
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) { c[i] = 0.f; sn[i] = 0.f; }
+    }
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const float partner = __shfl_xor_sync(0xffffffffu, v[i], 4);
       const float rot = lane8 < 4 ? -partner : partner;
-      float c = 0.f, sn = 0.f;
-      if (live) { c = (float)cos_t[t + i]; sn = (float)sin_t[t + i]; }
-      const float pc = __bfloat162float(__float2bfloat16_rn(__fmul_rn(v[i], c)));
-      const float qs = __bfloat162float(__float2bfloat16_rn(__fmul_rn(rot, sn)));
+      const float pc = __bfloat162float(__float2bfloat16_rn(__fmul_rn(v[i], c[i])));
+      const float qs = __bfloat162float(__float2bfloat16_rn(__fmul_rn(rot, sn[i])));
       v[i] = __fadd_rn(pc, qs);
     }
   }
@@ -298,7 +321,8 @@ extern "C" int tw_rope_heads(const void* x, void* y, long long tokens, int heads
                              const void* cos_table, const void* sin_table, long long table_rows, int table_is_bf16, int norm,
                              float eps, void* stream_) {
   if (!x || !y || !cos_table || !sin_table || tokens <= 0 || heads <= 0 || table_rows <= 0) return TW_ERR_ARGUMENT;
-  if (misaligned(x) || misaligned(y) || ((stride_token | stride_head) & 7)) return TW_ERR_ALIGNMENT;
+  if (misaligned(x) || misaligned(y) || misaligned(cos_table) || misaligned(sin_table) || ((stride_token | stride_head) & 7))
+    return TW_ERR_ALIGNMENT;
   const long long rows = tokens * heads;
   const unsigned grid = (unsigned)((rows + 31) / 32);
   cudaStream_t st = static_cast<cudaStream_t>(stream_);
