@@ -216,3 +216,16 @@ def test_cfg_parallel_rank_compiles_its_own_branch():
         engine.rows[('attention', '0', 1, ph)] = {**att, 'name': '0', 'branch': 1, 'phase': ph}
     ledger = engine.compile_budget()
     assert ledger['feasible'] and ledger['total_mma'] <= 2 * ledger['base_mma']
+
+
+def test_bench_topology_splits_cfg_branches_first():
+    """The benchmark's layout per GPU count: one GPU, then one CFG branch per GPU, then tensor parallelism inside
+    each branch; `--cfg-parallel 1` forces tensor parallelism alone."""
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), 'bench.py')
+    spec = importlib.util.spec_from_file_location('bench_module_for_test', path)
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    assert [bench.step_topology(n, 0) for n in (1, 2, 4, 8)] == [(1, 1), (1, 2), (2, 2), (4, 2)]
+    assert [bench.step_topology(n, 1) for n in (2, 4)] == [(2, 1), (4, 1)]
