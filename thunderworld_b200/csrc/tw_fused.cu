@@ -422,8 +422,12 @@ fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ 
           tw::tc_commit(emptyS + s);
         }
         __syncwarp();
-        sa = (sa + __popc(units & 9u)) % C::A1_SLOTS;
-        sw = (sw + __popc(units & 54u)) % C::W1_SLOTS;
+        // ring positions advance by at most one ring length per step: a conditional subtract, not a modulo (this
+        // warp's instruction stream is the kernel's critical path)
+        sa += __popc(units & 9u);
+        if (sa >= (uint32_t)C::A1_SLOTS) sa -= C::A1_SLOTS;
+        sw += __popc(units & 54u);
+        if (sw >= (uint32_t)C::W1_SLOTS) sw -= C::W1_SLOTS;
         if (++s == C::STAGES) { s = 0; ph ^= 1; }
         abits >>= 2;
 #pragma unroll
